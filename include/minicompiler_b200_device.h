@@ -1,0 +1,169 @@
+/* Thin C-ABI device layer of minicompiler-b200.
+ *
+ * Everything the C++17 host side (lowering, planner, executable, C API) needs
+ * from CUDA goes through these calls: plain pointers, integers and opaque
+ * handles only, so no CUDA or C++ type crosses the line and the layer can be
+ * replaced by a fake in host-only tests. It takes the place of the direct
+ * CUDA-runtime / driver / NVRTC calls the reference makes from
+ * src/cuda/cuda_backend.cpp:154-257, src/cuda/kernel_compiler.cpp:24-57,
+ * src/cuda/device_info.cpp:33-73 and src/cuda/matmul_kernels.hpp:46-59.
+ *
+ * Conventions: every call returns 0 on success; on failure it returns non-zero
+ * and mcd_last_error() (thread-local) describes it as "<call>: <CUDA text>".
+ * `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ * stream). Unless stated otherwise calls act on the current device
+ * (mcd_set_device).
+ */
+#ifndef MINICOMPILER_B200_DEVICE_H
+#define MINICOMPILER_B200_DEVICE_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MCD_API __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------- device query
+ * Replaces query_device / current_sm_clock_mhz (src/cuda/device_info.cpp:33-73). */
+typedef struct mcd_device_info {
+    char name[128];
+    int cc_major;
+    int cc_minor;
+    int sm_count;
+    int fp32_lanes_per_sm;
+    double sm_clock_mhz;
+    double max_sm_clock_mhz; /* NVML; 0 when unavailable */
+    double mem_clock_mhz;
+    int bus_width_bits;
+    unsigned long long total_memory;
+    int runtime_version;
+    int driver_version;
+    int max_smem_per_block_optin;
+} mcd_device_info;
+
+MCD_API const char* mcd_last_error(void);
+MCD_API int mcd_device_count(int* count);
+MCD_API int mcd_query_device(int device, mcd_device_info* out);
+MCD_API double mcd_current_sm_clock_mhz(int device);
+MCD_API int mcd_set_device(int device);
+
+/* ------------------------------------------------------- memory and streams
+ * Replaces DeviceBuffer / cudaMemcpy* / stream handling
+ * (src/cuda/cuda_backend.cpp:56-78, :154-165, :186-196, :217-219). */
+MCD_API int mcd_malloc(void** ptr, size_t bytes);
+MCD_API int mcd_free(void* ptr);
+MCD_API int mcd_memset(void* ptr, int byte, size_t bytes, void* stream);
+MCD_API int mcd_copy_h2d(void* dst, const void* src, size_t bytes, void* stream);
+MCD_API int mcd_copy_d2h(void* dst, const void* src, size_t bytes, void* stream);
+MCD_API int mcd_copy_d2d(void* dst, const void* src, size_t bytes, void* stream);
+MCD_API int mcd_host_register(void* ptr, size_t bytes);   /* pin caller memory (optional fast path) */
+MCD_API int mcd_host_unregister(void* ptr);
+MCD_API int mcd_stream_create(void** stream);
+MCD_API int mcd_stream_destroy(void* stream);
+MCD_API int mcd_stream_synchronize(void* stream);
+MCD_API int mcd_device_synchronize(void);
+MCD_API int mcd_event_create(void** event);
+MCD_API int mcd_event_destroy(void* event);
+MCD_API int mcd_event_record(void* event, void* stream);
+MCD_API int mcd_event_elapsed_ms(void* start, void* stop, float* ms); /* waits for `stop` */
+
+/* -------------------------------------------------------- run-time kernels
+ * Replaces KernelCompiler::get + cuLaunchKernel + the occupancy query
+ * (src/cuda/kernel_compiler.cpp:24-57, src/cuda/cuda_backend.cpp:174-175,
+ * :311-317). Compiles CUDA C++ to an sm_100a cubin with NVRTC and loads it
+ * into `device`'s primary context; results are cached process-wide, keyed by
+ * (device, options, source, kernel name), so a kernel is never launched on a
+ * device other than the one its module was loaded for. */
+MCD_API int mcd_jit_kernel(int device, const char* source, const char* kernel_name, const char* options,
+                           void** function, double* compile_ms);
+MCD_API int mcd_jit_occupancy(void* function, int block_threads, size_t dynamic_smem, int* blocks_per_sm);
+MCD_API int mcd_jit_set_dynamic_smem(void* function, size_t bytes);
+MCD_API int mcd_launch(void* function, unsigned grid_x, unsigned grid_y, unsigned grid_z, unsigned block_x,
+                       size_t dynamic_smem, void* stream, void** params);
+/* Number of kernel launches issued through this layer by the calling process. */
+MCD_API unsigned long long mcd_launch_count(void);
+
+/* ------------------------------------------------------- built-in kernels */
+
+/* 16-bit formats of tensor-core operands. */
+#define MCD_HALF_BF16 1
+#define MCD_HALF_F16 2
+
+/* dst[r*dst_pitch + c] = round-to-nearest-even(src[r*src_pitch + c]) for an
+ * [rows, cols] matrix, or dst[c*dst_pitch + r] when `transpose` is non-zero.
+ * This is the rounding the reference applies while staging tiles
+ * (src/cuda/matmul_tensor_core.cu:45-57), done once per tensor instead. */
+MCD_API int mcd_cast_f32_to_half(int half_kind, const float* src, void* dst, long long rows, long long cols,
+                                 long long src_pitch, long long dst_pitch, int transpose, void* stream);
+/* dst[c*dst_pitch + r] = src[r*src_pitch + c] in fp32 (operand re-layout for TF32). */
+MCD_API int mcd_transpose_f32(const float* src, float* dst, long long rows, long long cols, long long src_pitch,
+                              long long dst_pitch, void* stream);
+
+/* Arithmetic of a matmul launch. */
+#define MCD_GEMM_F32 0  /* FP32 FMA, exact path */
+#define MCD_GEMM_TF32 1 /* tcgen05 kind::tf32 */
+#define MCD_GEMM_BF16 2 /* tcgen05 kind::f16, bf16 operands */
+#define MCD_GEMM_F16 3  /* tcgen05 kind::f16, fp16 operands */
+
+/* Up to 6 extra operands of a fused epilogue. */
+#define MCD_MAX_EPILOGUE_INPUTS 6
+
+/* One matmul launch, C[m,n] = epilogue(A[m,k] * B[k,n]); replaces launch_matmul
+ * (src/cuda/matmul_kernels.hpp:46-48) and its split-K helpers (:17-59).
+ *
+ *  a, b        operands. MCD_GEMM_F32 / TF32: float, row-major, leading dimensions lda/ldb in
+ *              elements. BF16/F16: 16-bit, same layouts. When `b_transposed` is non-zero, b holds
+ *              B^T, i.e. [n,k] row-major with leading dimension ldb.
+ *  c, c16      outputs: float [m,n] with leading dimension ldc (may be NULL) and/or a 16-bit copy
+ *              of kind `c16_kind` with leading dimension ldc16 (may be NULL).
+ *  splits      > 1 divides K; partial sums go to `workspace` (splits*m*n floats) and are added in a
+ *              fixed order, so results do not depend on scheduling.
+ *  function    NULL: the built-in kernel without epilogue. Otherwise a kernel obtained from
+ *              mcd_jit_kernel for the source returned by mcd_gemm_source(arith) with a generated
+ *              `mc_epilogue`; `epilogue_inputs` are its extra operands.
+ *  reduce_function  same, for the split-K reduction kernel (mcd_gemm_source(-1)).
+ */
+typedef struct mcd_gemm_args {
+    int arith;
+    int m, n, k;
+    const void* a;
+    const void* b;
+    long long lda, ldb;
+    int b_transposed;
+    float* c;
+    long long ldc;
+    void* c16;
+    int c16_kind;
+    long long ldc16;
+    int splits;
+    float* workspace;
+    void* function;
+    void* reduce_function;
+    const float* epilogue_inputs[MCD_MAX_EPILOGUE_INPUTS];
+    int num_epilogue_inputs;
+    unsigned int* status; /* device word: a kernel that gives up a bounded wait ORs an error code in */
+    int variant;          /* tuning variant, 0 = default */
+} mcd_gemm_args;
+
+MCD_API int mcd_gemm(const mcd_gemm_args* args, void* stream);
+/* Kernel launches one mcd_gemm call issues (1, or 2 when it splits K). */
+MCD_API int mcd_gemm_launches(const mcd_gemm_args* args);
+/* CUDA C++ source of a GEMM kernel family, for epilogue specialisation: the caller puts a
+ * generated `mc_epilogue` in front of it and compiles it with mcd_jit_kernel.
+ * arith = MCD_GEMM_*, or -1 for the split-K reduction. */
+MCD_API const char* mcd_gemm_source(int arith);
+/* The entry point inside that source which mcd_gemm would launch for `args` (it depends on the
+ * arithmetic, on operand alignment and on the layout of B); NULL args: the reduction kernel. */
+MCD_API const char* mcd_gemm_entry_point(const mcd_gemm_args* args);
+/* Dynamic shared memory the entry point needs (set it with mcd_jit_set_dynamic_smem). */
+MCD_API size_t mcd_gemm_dynamic_smem(int arith);
+/* Whether tcgen05 kernels can run on `device` (compute capability 10.x). */
+MCD_API int mcd_tensor_core_supported(int device, int arith);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MINICOMPILER_B200_DEVICE_H */

@@ -1,0 +1,520 @@
+#include "backend/b200_backend.hpp"
+
+#include "minicompiler_b200_device.h"
+
+#include <algorithm>
+#include <cstring>
+
+namespace minicompiler {
+
+std::vector<std::string> available_backends() { return {"cuda"}; }
+
+Result<std::unique_ptr<Backend>> create_backend(std::string_view name) {
+    if (name == "cuda") return cuda::make_cuda_backend();
+    if (name == "cpu") {
+        return Error{"this library replaces the CUDA backend only and has no CPU execution path (available: cuda)"};
+    }
+    return Error{"unknown backend '" + std::string(name) + "' (available: cuda)"};
+}
+
+namespace cuda {
+
+namespace {
+
+Status device_error(const char* what) { return Error{std::string(what) + ": " + mcd_last_error()}; }
+
+#define MCD_TRY(call)                                  \
+    do {                                               \
+        if ((call) != 0) return device_error(#call);   \
+    } while (0)
+
+constexpr std::size_t kAlign = 256;
+std::size_t align_up(std::size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+struct Launch {
+    enum class Kind { Elementwise, Matmul, Recast } kind = Kind::Elementwise;
+    // Elementwise: an NVRTC-compiled kernel; params = [out] [out16] in... n
+    void* function = nullptr;
+    unsigned grid = 0;
+    unsigned count = 0;
+    std::vector<void*> pointers;
+    std::vector<void*> params;
+    // Matmul
+    mcd_gemm_args gemm{};
+    MatmulKernel reported = MatmulKernel::DoubleBuffered;
+    // Recast: FP32 form -> another form
+    const float* src = nullptr;
+    void* dst = nullptr;
+    long long rows = 0, cols = 0, src_pitch = 0, dst_pitch = 0;
+    int transpose = 0;
+    int half_kind = 0;  // 0: FP32 transpose
+};
+
+class B200Executable final : public CudaExecutable {
+public:
+    static Result<std::unique_ptr<B200Executable>> create(const Graph& graph, const CudaOptions& options) {
+        std::unique_ptr<B200Executable> exe(new B200Executable(graph, options));
+        Status st = exe->init();
+        if (!st.ok()) return st.error();
+        return exe;
+    }
+
+    ~B200Executable() override {
+        if (arena_ != nullptr || stream_ != nullptr) mcd_set_device(options_.device);
+        if (stream_ != nullptr) mcd_stream_destroy(stream_);
+        if (arena_ != nullptr) mcd_free(arena_);
+    }
+
+    Status run(const std::vector<HostTensor>& inputs, std::vector<HostTensor>& outputs) override {
+        if (static_cast<const void*>(&inputs) == static_cast<const void*>(&outputs)) {
+            return Error{"run() needs separate input and output vectors"};
+        }
+        if (inputs.size() != graph_.inputs().size()) {
+            return Error{"expected " + std::to_string(graph_.inputs().size()) + " inputs, got " +
+                         std::to_string(inputs.size())};
+        }
+        std::vector<const float*> in;
+        for (std::size_t k = 0; k < inputs.size(); ++k) {
+            const Node& node = graph_.node(graph_.inputs()[k]);
+            if (inputs[k].type != node.type || inputs[k].data.size() != node.type.num_elements()) {
+                return Error{"input '" + node.name + "' should be " + to_string(node.type) + ", got " +
+                             to_string(inputs[k].type)};
+            }
+            in.push_back(inputs[k].data.data());
+        }
+        outputs.resize(graph_.outputs().size());
+        std::vector<float*> out;
+        for (std::size_t k = 0; k < outputs.size(); ++k) {
+            const TensorType& type = graph_.node(graph_.outputs()[k]).type;
+            outputs[k].type = type;
+            outputs[k].data.resize(type.num_elements());
+            out.push_back(outputs[k].data.data());
+        }
+        return run_buffers(in, out);
+    }
+
+    Status run_buffers(const std::vector<const float*>& inputs, const std::vector<float*>& outputs) override {
+        if (inputs.size() != graph_.inputs().size() || outputs.size() != graph_.outputs().size()) {
+            return Error{"expected " + std::to_string(graph_.inputs().size()) + " input and " +
+                         std::to_string(graph_.outputs().size()) + " output buffers"};
+        }
+        MC_TRY(upload_inputs(inputs));
+        MC_TRY(enqueue(nullptr));
+        return download_outputs(outputs);
+    }
+
+    std::size_t intermediate_bytes() const override { return lowered_.pool.bytes_with_reuse(); }
+
+    Status upload_inputs(const std::vector<const float*>& host_inputs) override {
+        if (host_inputs.size() != graph_.inputs().size()) return Error{"wrong number of inputs"};
+        MCD_TRY(mcd_set_device(options_.device));
+        for (std::size_t k = 0; k < host_inputs.size(); ++k) {
+            const NodeId id = graph_.inputs()[k];
+            MCD_TRY(mcd_copy_h2d(address(id, kRepF32), host_inputs[k], graph_.node(id).type.size_bytes(), stream_));
+        }
+        for (const Launch& l : upload_recasts_) MC_TRY(issue(l, stream_));
+        // Kernels may be enqueued on another stream, which would not wait for these copies.
+        MCD_TRY(mcd_stream_synchronize(stream_));
+        return Status();
+    }
+
+    Status enqueue(void* stream) override {
+        void* s = stream != nullptr ? stream : stream_;
+        for (const std::unique_ptr<Launch>& l : launches_) MC_TRY(issue(*l, s));
+        return Status();
+    }
+
+    Status synchronize() override {
+        MCD_TRY(mcd_set_device(options_.device));
+        MCD_TRY(mcd_device_synchronize());
+        return check_status_word();
+    }
+
+    Status download_outputs(const std::vector<float*>& host_outputs) override {
+        if (host_outputs.size() != graph_.outputs().size()) return Error{"wrong number of outputs"};
+        MCD_TRY(mcd_set_device(options_.device));
+        MCD_TRY(mcd_device_synchronize());  // kernels may sit on a caller's stream
+        MC_TRY(check_status_word());
+        for (std::size_t k = 0; k < host_outputs.size(); ++k) {
+            const NodeId id = graph_.outputs()[k];
+            MCD_TRY(mcd_copy_d2h(host_outputs[k], address(id, kRepF32), graph_.node(id).type.size_bytes(), stream_));
+        }
+        MCD_TRY(mcd_stream_synchronize(stream_));
+        return Status();
+    }
+
+    std::size_t kernel_launches() const override { return lowered_.kernel_launches; }
+    std::vector<std::string> kernel_sources() const override { return sources_; }
+    std::vector<MatmulKernel> matmul_kernels() const override {
+        std::vector<MatmulKernel> kernels;
+        for (const std::unique_ptr<Launch>& l : launches_) {
+            if (l->kind == Launch::Kind::Matmul) kernels.push_back(l->reported);
+        }
+        return kernels;
+    }
+    double jit_compile_ms() const override { return jit_ms_; }
+
+    void constants_region(void** ptr, std::size_t* bytes) const override {
+        *ptr = arena_;
+        *bytes = constants_bytes_;
+    }
+
+    Status refresh_constants() override {
+        MCD_TRY(mcd_set_device(options_.device));
+        for (const Launch& l : constant_recasts_) MC_TRY(issue(l, stream_));
+        MCD_TRY(mcd_stream_synchronize(stream_));
+        return Status();
+    }
+
+    std::size_t arena_bytes() const override { return arena_bytes_; }
+    std::string plan_description() const override { return describe(graph_, lowered_); }
+
+    void output_buffer(std::size_t k, void** ptr, std::size_t* elements) const override {
+        const NodeId id = graph_.outputs()[k];
+        *ptr = address(id, kRepF32);
+        *elements = graph_.node(id).type.num_elements();
+    }
+    void input_buffer(std::size_t k, void** ptr, std::size_t* elements) const override {
+        const NodeId id = graph_.inputs()[k];
+        *ptr = address(id, kRepF32);
+        *elements = graph_.node(id).type.num_elements();
+    }
+
+private:
+    B200Executable(const Graph& graph, const CudaOptions& options) : graph_(graph), options_(options) {}
+
+    char* address(NodeId id, Rep rep) const {
+        const std::size_t slot = static_cast<std::size_t>(id) * kNumReps + static_cast<std::size_t>(rep);
+        return offset_[slot] == kNoOffset ? nullptr : static_cast<char*>(arena_) + offset_[slot];
+    }
+
+    Status check_status_word() {
+        if (!uses_status_) return Status();
+        unsigned word = 0;
+        MCD_TRY(mcd_copy_d2h(&word, status_word(), sizeof word, stream_));
+        MCD_TRY(mcd_stream_synchronize(stream_));
+        if (word != 0) {
+            MCD_TRY(mcd_memset(status_word(), 0, sizeof word, stream_));
+            return Error{"a tensor-core matmul gave up a bounded wait (status 0x" + to_hex(word) +
+                         "): results of this run are incomplete"};
+        }
+        return Status();
+    }
+
+    static std::string to_hex(unsigned v) {
+        char text[16];
+        std::snprintf(text, sizeof text, "%x", v);
+        return text;
+    }
+
+    unsigned* status_word() const { return reinterpret_cast<unsigned*>(static_cast<char*>(arena_) + status_offset_); }
+
+    Status issue(const Launch& l, void* stream) const {
+        switch (l.kind) {
+            case Launch::Kind::Elementwise:
+                MCD_TRY(mcd_launch(l.function, l.grid, 1, 1, kElementwiseBlock, 0, stream, const_cast<void**>(l.params.data())));
+                return Status();
+            case Launch::Kind::Matmul: MCD_TRY(mcd_gemm(&l.gemm, stream)); return Status();
+            case Launch::Kind::Recast:
+                if (l.half_kind == 0) {
+                    MCD_TRY(mcd_transpose_f32(l.src, static_cast<float*>(l.dst), l.rows, l.cols, l.src_pitch, l.dst_pitch, stream));
+                } else {
+                    MCD_TRY(mcd_cast_f32_to_half(l.half_kind, l.src, l.dst, l.rows, l.cols, l.src_pitch, l.dst_pitch,
+                                                 l.transpose, stream));
+                }
+                return Status();
+        }
+        return Status();
+    }
+
+    Launch make_recast(const Recast& rc) const {
+        const TensorType& type = graph_.node(rc.node).type;
+        Launch l;
+        l.kind = Launch::Kind::Recast;
+        l.src = reinterpret_cast<const float*>(address(rc.node, kRepF32));
+        l.dst = address(rc.node, rc.to);
+        l.rows = type.shape[0];
+        l.cols = type.shape[1];
+        l.src_pitch = l.cols;
+        const int half = lowered_.half_kind == HalfKind::Bf16 ? MCD_HALF_BF16 : MCD_HALF_F16;
+        switch (rc.to) {
+            case kRepHalf:
+                l.half_kind = half;
+                l.dst_pitch = half_pitch(l.cols);
+                break;
+            case kRepHalfT:
+                l.half_kind = half;
+                l.transpose = 1;
+                l.dst_pitch = half_pitch(l.rows);
+                break;
+            default:  // kRepF32T
+                l.half_kind = 0;
+                l.transpose = 1;
+                l.dst_pitch = (l.rows + 3) / 4 * 4;
+                break;
+        }
+        return l;
+    }
+
+    Status init() {
+        Result<DeviceInfo> device = query_device(options_.device);
+        if (!device.ok()) return device.error();
+        device_ = std::move(device).value();
+        if (device_.cc_major != 10) {
+            return Error{"this backend is built for sm_100a (B200) only; device " + std::to_string(options_.device) + " is " +
+                         device_.name + " (compute capability " + std::to_string(device_.cc_major) + "." +
+                         std::to_string(device_.cc_minor) + ")"};
+        }
+        MCD_TRY(mcd_set_device(options_.device));
+        MCD_TRY(mcd_stream_create(&stream_));
+
+        MC_ASSIGN(lowered, lower_graph(graph_, options_, device_.sm_count));
+        lowered_ = std::move(lowered);
+
+        // ---- arena layout: constants | inputs | pooled buffers | split-K workspace | status word
+        const std::size_t count = graph_.num_nodes();
+        offset_.assign(count * kNumReps, kNoOffset);
+        std::size_t cursor = 0;
+        auto place_leaves = [&](OpKind kind) {
+            for (std::size_t i = 0; i < count; ++i) {
+                const Node& n = graph_.node(static_cast<NodeId>(i));
+                if (n.op != kind) continue;
+                for (int rep = 0; rep < kNumReps; ++rep) {
+                    if (!lowered_.needs[i][static_cast<std::size_t>(rep)]) continue;
+                    offset_[i * kNumReps + static_cast<std::size_t>(rep)] = cursor;
+                    cursor += align_up(rep_bytes(n.type, static_cast<Rep>(rep)));
+                }
+            }
+        };
+        place_leaves(OpKind::Constant);
+        constants_bytes_ = cursor;
+        place_leaves(OpKind::Input);
+        std::vector<std::size_t> buffer_offset(lowered_.pool.buffer_bytes.size());
+        for (std::size_t b = 0; b < buffer_offset.size(); ++b) {
+            buffer_offset[b] = cursor;
+            cursor += align_up(std::max<std::size_t>(lowered_.pool.buffer_bytes[b], sizeof(float)));
+        }
+        for (std::size_t v = 0; v < lowered_.pool.buffer_of.size(); ++v) {
+            const std::int32_t b = lowered_.pool.buffer_of[v];
+            if (b != PoolPlan::kNotPooled) offset_[v] = buffer_offset[static_cast<std::size_t>(b)];
+        }
+        const std::size_t workspace_offset = cursor;
+        cursor += align_up(lowered_.workspace_bytes);
+        status_offset_ = cursor;
+        cursor += kAlign;
+        arena_bytes_ = cursor;
+        MCD_TRY(mcd_malloc(&arena_, arena_bytes_));
+        MCD_TRY(mcd_memset(status_word(), 0, kAlign, stream_));
+        float* workspace = lowered_.workspace_bytes > 0 ? reinterpret_cast<float*>(static_cast<char*>(arena_) + workspace_offset)
+                                                        : nullptr;
+
+        // ---- constants: uploaded once, derived forms made once
+        for (std::size_t i = 0; i < count; ++i) {
+            const Node& n = graph_.node(static_cast<NodeId>(i));
+            if (n.op != OpKind::Constant) continue;
+            MCD_TRY(mcd_copy_h2d(address(static_cast<NodeId>(i), kRepF32), n.constant->data(), n.type.size_bytes(), stream_));
+        }
+        for (const Recast& rc : lowered_.at_compile) constant_recasts_.push_back(make_recast(rc));
+        for (const Recast& rc : lowered_.after_upload) upload_recasts_.push_back(make_recast(rc));
+        for (const Launch& l : constant_recasts_) MC_TRY(issue(l, stream_));
+        MCD_TRY(mcd_stream_synchronize(stream_));
+
+        // ---- launches
+        for (std::size_t i = 0; i < lowered_.steps.size(); ++i) {
+            const Step& step = lowered_.steps[i];
+            if (step.kind == Step::Kind::Elementwise) {
+                MC_TRY(add_elementwise(step));
+            } else {
+                MC_TRY(add_matmul(step, workspace));
+            }
+            for (const Recast& rc : lowered_.after_step[i]) launches_.push_back(std::make_unique<Launch>(make_recast(rc)));
+        }
+        return Status();
+    }
+
+    Status add_elementwise(const Step& step) {
+        const Node& node = graph_.node(step.result);
+        std::vector<Shape> shapes;
+        for (NodeId in : step.inputs) shapes.push_back(graph_.node(in).type.shape);
+        ElementwiseOptions eo;
+        eo.allow_vectorize = options_.vectorize;
+        eo.unroll = options_.eltwise_unroll;
+        eo.write_f32 = step.write_f32;
+        eo.write_half = step.write_half;
+        eo.streaming_hints = options_.streaming_hints;
+        if (step.write_half != HalfKind::None && node.type.shape.size() == 2) eo.half_pitch = half_pitch(node.type.shape[1]);
+        const ElementwiseKernel kernel = generate_elementwise_kernel(step.program, shapes, node.type.shape, eo);
+
+        auto launch = std::make_unique<Launch>();
+        launch->kind = Launch::Kind::Elementwise;
+        double ms = 0.0;
+        if (mcd_jit_kernel(options_.device, kernel.source.c_str(), kElementwiseKernelName, "--fmad=false", &launch->function,
+                           &ms) != 0) {
+            return Error{std::string("compiling the kernel of '") + node.name + "' failed: " + mcd_last_error()};
+        }
+        jit_ms_ += ms;
+        sources_.push_back(kernel.source);
+
+        const std::size_t n = node.type.num_elements();
+        launch->count = static_cast<unsigned>(kernel.vectorized ? n / 4 : n);
+        int blocks_per_sm = 0;
+        MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(kElementwiseBlock), 0, &blocks_per_sm));
+        // One wave of resident blocks at most; the tile loop inside the kernel covers the rest.
+        const std::size_t per_block = static_cast<std::size_t>(kElementwiseBlock) * kernel.unroll;
+        const std::size_t wanted = (launch->count + per_block - 1) / per_block;
+        const std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
+        launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(wanted, resident)));
+        if (kernel.has_f32_out) launch->pointers.push_back(address(step.result, kRepF32));
+        if (kernel.has_half_out) launch->pointers.push_back(address(step.result, kRepHalf));
+        for (NodeId in : step.inputs) launch->pointers.push_back(address(in, kRepF32));
+        for (void*& p : launch->pointers) launch->params.push_back(&p);
+        launch->params.push_back(&launch->count);
+        launches_.push_back(std::move(launch));
+        return Status();
+    }
+
+    Status add_matmul(const Step& step, float* workspace) {
+        auto launch = std::make_unique<Launch>();
+        launch->kind = Launch::Kind::Matmul;
+        launch->reported = step.kernel;
+        mcd_gemm_args& g = launch->gemm;
+        std::memset(&g, 0, sizeof g);
+        g.arith = static_cast<int>(step.arith);
+        g.m = step.m;
+        g.n = step.n;
+        g.k = step.k;
+        const bool half = step.arith == Arith::Bf16 || step.arith == Arith::F16;
+        if (is_tensor_core(step.kernel) && mcd_tensor_core_supported(options_.device, g.arith) == 0) {
+            return Error{std::string("matmul kernel '") + matmul_kernel_name(step.kernel) + "' does not run on " + device_.name +
+                         ": the tcgen05 kernels need compute capability 10.x"};
+        }
+        g.a = address(step.lhs, half ? kRepHalf : kRepF32);
+        g.lda = half ? half_pitch(step.k) : step.k;
+        if (step.rhs_transposed) {
+            g.b = address(step.rhs, half ? kRepHalfT : kRepF32T);
+            g.ldb = half ? half_pitch(step.k) : (step.k + 3) / 4 * 4;
+            g.b_transposed = 1;
+        } else {
+            g.b = address(step.rhs, half ? kRepHalf : kRepF32);
+            g.ldb = half ? half_pitch(step.n) : step.n;
+        }
+        g.c = step.write_f32 ? reinterpret_cast<float*>(address(step.result, kRepF32)) : nullptr;
+        g.ldc = step.n;
+        if (step.write_half != HalfKind::None) {
+            g.c16 = address(step.result, kRepHalf);
+            g.c16_kind = step.write_half == HalfKind::Bf16 ? MCD_HALF_BF16 : MCD_HALF_F16;
+            g.ldc16 = half_pitch(step.n);
+        }
+        g.splits = step.splits;
+        g.workspace = step.splits > 1 ? workspace : nullptr;
+        g.variant = options_.gemm_variant;
+        if (is_tensor_core(step.kernel)) {
+            g.status = status_word();
+            uses_status_ = true;
+        }
+        if (step.has_epilogue) {
+            int slot = 0;
+            for (std::size_t k = 0; k < step.inputs.size(); ++k) {
+                if (step.load_is_accumulator[k]) continue;
+                g.epilogue_inputs[slot++] = reinterpret_cast<const float*>(address(step.inputs[k], kRepF32));
+            }
+            g.num_epilogue_inputs = slot;
+            const std::string epilogue = generate_epilogue_source(graph_, step);
+            sources_.push_back(epilogue);
+            double ms = 0.0;
+            if (mcd_gemm_launches(&g) > 1) {
+                // K is split: the main kernel writes raw partial sums, the reduction applies the epilogue.
+                const std::string source = epilogue + mcd_gemm_source(-1);
+                if (mcd_jit_kernel(options_.device, source.c_str(), mcd_gemm_entry_point(nullptr), "--fmad=false",
+                                   &g.reduce_function, &ms) != 0) {
+                    return Error{std::string("compiling the epilogue of '") + graph_.node(step.result).name +
+                                 "' failed: " + mcd_last_error()};
+                }
+            } else {
+                const std::string source = epilogue + mcd_gemm_source(g.arith);
+                if (mcd_jit_kernel(options_.device, source.c_str(), mcd_gemm_entry_point(&g), "--fmad=false", &g.function,
+                                   &ms) != 0) {
+                    return Error{std::string("compiling the epilogue of '") + graph_.node(step.result).name +
+                                 "' failed: " + mcd_last_error()};
+                }
+                const std::size_t smem = mcd_gemm_dynamic_smem(g.arith);
+                if (smem > 0) MCD_TRY(mcd_jit_set_dynamic_smem(g.function, smem));
+            }
+            jit_ms_ += ms;
+        }
+        launches_.push_back(std::move(launch));
+        return Status();
+    }
+
+    static constexpr std::size_t kNoOffset = static_cast<std::size_t>(-1);
+
+    Graph graph_;
+    CudaOptions options_;
+    DeviceInfo device_;
+    LoweredGraph lowered_;
+    void* stream_ = nullptr;
+    void* arena_ = nullptr;
+    std::size_t arena_bytes_ = 0;
+    std::size_t constants_bytes_ = 0;
+    std::size_t status_offset_ = 0;
+    bool uses_status_ = false;
+    std::vector<std::size_t> offset_;  // per (node, rep): byte offset in the arena
+    std::vector<std::unique_ptr<Launch>> launches_;
+    std::vector<Launch> upload_recasts_;
+    std::vector<Launch> constant_recasts_;
+    std::vector<std::string> sources_;
+    double jit_ms_ = 0.0;
+};
+
+class B200Backend final : public Backend {
+public:
+    explicit B200Backend(const CudaOptions& options) : options_(options) {}
+    const char* name() const override { return "cuda"; }
+    Result<std::unique_ptr<Executable>> compile(const Graph& graph) override {
+        Result<std::unique_ptr<CudaExecutable>> exe = compile_for_cuda(graph, options_);
+        if (!exe.ok()) return exe.error();
+        return std::unique_ptr<Executable>(std::move(exe).value());
+    }
+
+private:
+    CudaOptions options_;
+};
+
+}  // namespace
+
+Result<DeviceInfo> query_device(int device) {
+    mcd_device_info raw;
+    if (mcd_query_device(device, &raw) != 0) return Error{mcd_last_error()};
+    DeviceInfo info;
+    info.name = raw.name;
+    info.cc_major = raw.cc_major;
+    info.cc_minor = raw.cc_minor;
+    info.sm_count = raw.sm_count;
+    info.fp32_lanes_per_sm = raw.fp32_lanes_per_sm;
+    info.sm_clock_mhz = raw.sm_clock_mhz;
+    info.max_sm_clock_mhz = raw.max_sm_clock_mhz;
+    info.mem_clock_mhz = raw.mem_clock_mhz;
+    info.bus_width_bits = raw.bus_width_bits;
+    info.total_memory = raw.total_memory;
+    info.runtime_version = raw.runtime_version;
+    info.driver_version = raw.driver_version;
+    return info;
+}
+
+double current_sm_clock_mhz(int device) { return mcd_current_sm_clock_mhz(device); }
+
+Result<std::unique_ptr<CudaExecutable>> compile_for_cuda(const Graph& graph, const CudaOptions& options) {
+    MC_TRY(graph.verify());
+    Result<std::unique_ptr<B200Executable>> exe = B200Executable::create(graph, options);
+    if (!exe.ok()) return exe.error();
+    return std::unique_ptr<CudaExecutable>(std::move(exe).value());
+}
+
+Result<std::unique_ptr<Backend>> make_cuda_backend(const CudaOptions& options) {
+    Result<DeviceInfo> device = query_device(options.device);
+    if (!device.ok()) return Error{"no usable CUDA device: " + device.error().message};
+    return std::unique_ptr<Backend>(std::make_unique<B200Backend>(options));
+}
+
+}  // namespace cuda
+}  // namespace minicompiler

@@ -1,0 +1,408 @@
+#include "backend/lowering.hpp"
+
+#include <algorithm>
+#include <array>
+#include <cstdio>
+#include <sstream>
+
+namespace minicompiler::cuda {
+
+// ------------------------------------------------------- kernel vocabulary
+
+namespace {
+
+constexpr MatmulKernel kAllKernels[] = {
+    MatmulKernel::Auto,           MatmulKernel::Naive,          MatmulKernel::Tiled,
+    MatmulKernel::RegisterTiled128, MatmulKernel::RegisterTiled64, MatmulKernel::Vectorized,
+    MatmulKernel::DoubleBuffered, MatmulKernel::SplitK,         MatmulKernel::TensorCoreTf32,
+    MatmulKernel::TensorCoreBf16, MatmulKernel::TensorCoreF16,
+};
+
+}  // namespace
+
+const char* matmul_kernel_name(MatmulKernel kernel) {
+    switch (kernel) {
+        case MatmulKernel::Auto: return "auto";
+        case MatmulKernel::Naive: return "naive";
+        case MatmulKernel::Tiled: return "tiled";
+        case MatmulKernel::RegisterTiled128: return "register_tiled_128";
+        case MatmulKernel::RegisterTiled64: return "register_tiled_64";
+        case MatmulKernel::Vectorized: return "vectorized";
+        case MatmulKernel::DoubleBuffered: return "double_buffered";
+        case MatmulKernel::SplitK: return "split_k";
+        case MatmulKernel::TensorCoreTf32: return "tensor_core_tf32";
+        case MatmulKernel::TensorCoreBf16: return "tensor_core_bf16";
+        case MatmulKernel::TensorCoreF16: return "tensor_core_f16";
+    }
+    return "?";
+}
+
+Result<MatmulKernel> matmul_kernel_from_name(const std::string& name) {
+    std::string known;
+    for (MatmulKernel k : kAllKernels) {
+        if (name == matmul_kernel_name(k)) return k;
+        known += (known.empty() ? "" : ", ") + std::string(matmul_kernel_name(k));
+    }
+    return Error{"unknown matmul kernel '" + name + "' (" + known + ")"};
+}
+
+bool is_tensor_core(MatmulKernel kernel) {
+    return kernel == MatmulKernel::TensorCoreTf32 || kernel == MatmulKernel::TensorCoreBf16 ||
+           kernel == MatmulKernel::TensorCoreF16;
+}
+
+bool uses_split_k(MatmulKernel kernel) { return kernel == MatmulKernel::SplitK || is_tensor_core(kernel); }
+
+int split_k_splits(int m, int n, int k, int sm_count, int blocks_per_sm) {
+    const std::int64_t tiles = ((static_cast<std::int64_t>(m) + 127) / 128) * ((static_cast<std::int64_t>(n) + 127) / 128);
+    const std::int64_t sms = sm_count;
+    if (5 * tiles >= 4 * sms) return 1;  // the output alone covers 80% of the SMs
+    // Up to half the SMs' worth of tiles: aim for one block per SM. Between half and 80%: two per SM
+    // where an SM holds two blocks, otherwise still one.
+    std::int64_t splits = (2 * tiles <= sms || blocks_per_sm < 2) ? sms / tiles : 2 * sms / tiles;
+    splits = std::min<std::int64_t>(splits, k / 64);  // no split shorter than 64 along K
+    return static_cast<int>(std::max<std::int64_t>(splits, 1));
+}
+
+int tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes) {
+    const std::int64_t tiles = ((static_cast<std::int64_t>(m) + 127) / 128) * ((static_cast<std::int64_t>(n) + 255) / 256);
+    const std::int64_t sms = sm_count;
+    if (5 * tiles >= 4 * sms) return 1;
+    const std::int64_t block_k = 128 / elem_bytes;
+    const std::int64_t k_blocks = (k + block_k - 1) / block_k;
+    std::int64_t splits = std::min<std::int64_t>(sms / tiles, k_blocks / 4);  // at least 4 K blocks per work item
+    return static_cast<int>(std::max<std::int64_t>(splits, 1));
+}
+
+MatmulKernel resolve_matmul_kernel(MatmulKernel kernel, int m, int n, int k, int sm_count) {
+    if (kernel != MatmulKernel::Auto) return kernel;
+    return split_k_splits(m, n, k, sm_count) > 1 ? MatmulKernel::SplitK : MatmulKernel::DoubleBuffered;
+}
+
+int matmul_splits(MatmulKernel kernel, int m, int n, int k, int sm_count) {
+    if (kernel == MatmulKernel::SplitK) return split_k_splits(m, n, k, sm_count);
+    if (kernel == MatmulKernel::TensorCoreTf32) return tensor_core_splits(m, n, k, sm_count, 4);
+    if (is_tensor_core(kernel)) return tensor_core_splits(m, n, k, sm_count, 2);
+    return 1;
+}
+
+std::size_t matmul_workspace_bytes(MatmulKernel kernel, int m, int n, int splits) {
+    if (!uses_split_k(kernel) || splits <= 1) return 0;
+    return static_cast<std::size_t>(splits) * static_cast<std::size_t>(m) * static_cast<std::size_t>(n) * sizeof(float);
+}
+
+std::size_t rep_bytes(const TensorType& type, Rep rep) {
+    if (rep == kRepF32) return type.size_bytes();
+    // The other forms exist only for rank-2 matmul operands.
+    const std::int64_t rows = type.shape.size() == 2 ? type.shape[0] : 1;
+    const std::int64_t cols = type.shape.size() == 2 ? type.shape[1] : static_cast<std::int64_t>(type.num_elements());
+    switch (rep) {
+        case kRepHalf: return static_cast<std::size_t>(rows * half_pitch(cols)) * 2;
+        case kRepHalfT: return static_cast<std::size_t>(cols * half_pitch(rows)) * 2;
+        case kRepF32T: return static_cast<std::size_t>(cols * ((rows + 3) / 4 * 4)) * 4;
+        default: return type.size_bytes();
+    }
+}
+
+// ---------------------------------------------------------------- lowering
+
+namespace {
+
+// Can `operand` be read from inside a matmul epilogue over an [m,n] result?
+bool classify_epilogue_operand(const Shape& operand, const Shape& out, EpilogueOperand::Kind* kind) {
+    const Access a = classify_access(operand, out);
+    switch (a.kind) {
+        case AccessKind::Scalar: *kind = EpilogueOperand::Kind::Scalar; return true;
+        case AccessKind::Contiguous: *kind = EpilogueOperand::Kind::Full; return true;
+        case AccessKind::Periodic:
+            if (a.period != static_cast<std::size_t>(out[1])) return false;
+            *kind = EpilogueOperand::Kind::Row;
+            return true;
+        case AccessKind::General:
+            if (a.strides.size() == 2 && a.strides[0] == 1 && a.strides[1] == 0) {
+                *kind = EpilogueOperand::Kind::Column;
+                return true;
+            }
+            return false;
+    }
+    return false;
+}
+
+}  // namespace
+
+Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options, int sm_count) {
+    const std::size_t count = graph.num_nodes();
+    const std::vector<std::vector<NodeId>> users = graph.compute_users();
+    LoweredGraph out;
+    out.needs.assign(count, {false, false, false, false});
+    if (options.matmul == MatmulKernel::TensorCoreBf16) out.half_kind = HalfKind::Bf16;
+    if (options.matmul == MatmulKernel::TensorCoreF16) out.half_kind = HalfKind::F16;
+    const bool rhs_transposed = options.b_layout == BLayout::Transposed;
+
+    // Which matmul is folded into which consumer.
+    std::vector<NodeId> folded_into(count, kNoNode);  // matmul -> consumer
+    std::vector<NodeId> carries(count, kNoNode);      // consumer -> matmul
+    if (options.fuse_epilogue) {
+        for (std::size_t i = 0; i < count; ++i) {
+            const auto h = static_cast<NodeId>(i);
+            const Node& hn = graph.node(h);
+            if (hn.op != OpKind::MatMul || graph.is_output(h) || users[i].size() != 1) continue;
+            const NodeId u = users[i][0];
+            const Node& un = graph.node(u);
+            const bool elementwise_like = is_elementwise(un.op) || un.op == OpKind::FusedElementwise;
+            if (!elementwise_like || un.type.shape != hn.type.shape || carries[static_cast<std::size_t>(u)] != kNoNode) continue;
+            bool ok = true;
+            std::size_t extra = 0;
+            for (NodeId in : un.inputs) {
+                if (in == h) continue;
+                EpilogueOperand::Kind kind;
+                if (graph.node(in).op == OpKind::MatMul && folded_into[static_cast<std::size_t>(in)] == u) ok = false;
+                if (!classify_epilogue_operand(graph.node(in).type.shape, un.type.shape, &kind)) ok = false;
+                ++extra;
+            }
+            if (!ok || extra > 6) continue;
+            folded_into[i] = u;
+            carries[static_cast<std::size_t>(u)] = h;
+        }
+    }
+
+    auto make_matmul_step = [&](NodeId h) {
+        const Node& hn = graph.node(h);
+        const Shape& a = graph.node(hn.inputs[0]).type.shape;
+        Step s;
+        s.kind = Step::Kind::Matmul;
+        s.matmul = h;
+        s.result = h;
+        s.lhs = hn.inputs[0];
+        s.rhs = hn.inputs[1];
+        s.m = static_cast<int>(a[0]);
+        s.k = static_cast<int>(a[1]);
+        s.n = static_cast<int>(hn.type.shape[1]);
+        MatmulKernel kernel = resolve_matmul_kernel(options.matmul, s.m, s.n, s.k, sm_count);
+        // TF32 reads the FP32 tensors in place through TMA, which needs 16-byte row pitches.
+        if (kernel == MatmulKernel::TensorCoreTf32 && (s.k % 4 != 0 || s.n % 4 != 0)) {
+            kernel = resolve_matmul_kernel(MatmulKernel::Auto, s.m, s.n, s.k, sm_count);
+        }
+        s.kernel = kernel;
+        s.arith = kernel == MatmulKernel::TensorCoreTf32   ? Arith::Tf32
+                  : kernel == MatmulKernel::TensorCoreBf16 ? Arith::Bf16
+                  : kernel == MatmulKernel::TensorCoreF16  ? Arith::F16
+                                                           : Arith::F32;
+        s.splits = matmul_splits(kernel, s.m, s.n, s.k, sm_count);
+        s.rhs_transposed = is_tensor_core(kernel) && rhs_transposed;
+        s.launches = s.splits > 1 ? 2 : 1;
+        return s;
+    };
+
+    std::vector<std::int32_t> step_of(count, -1);
+    for (std::size_t i = 0; i < count; ++i) {
+        const auto id = static_cast<NodeId>(i);
+        const Node& n = graph.node(id);
+        if (!is_compute(n.op)) continue;
+        if (n.op == OpKind::MatMul) {
+            if (folded_into[i] != kNoNode) continue;  // emitted with its consumer
+            out.steps.push_back(make_matmul_step(id));
+        } else if (carries[i] != kNoNode) {
+            Step s = make_matmul_step(carries[i]);
+            s.result = id;
+            s.has_epilogue = true;
+            s.program = n.op == OpKind::FusedElementwise ? *n.fused : single_op_program(n.op);
+            s.inputs = n.inputs;
+            for (NodeId in : n.inputs) {
+                EpilogueOperand operand;
+                operand.node = in;
+                const bool is_acc = in == carries[i];
+                s.load_is_accumulator.push_back(is_acc ? 1 : 0);
+                if (!is_acc) classify_epilogue_operand(graph.node(in).type.shape, n.type.shape, &operand.kind);
+                s.operands.push_back(operand);
+            }
+            out.steps.push_back(std::move(s));
+        } else {
+            Step s;
+            s.kind = Step::Kind::Elementwise;
+            s.result = id;
+            s.program = n.op == OpKind::FusedElementwise ? *n.fused : single_op_program(n.op);
+            s.inputs = n.inputs;
+            out.steps.push_back(std::move(s));
+        }
+        step_of[i] = static_cast<std::int32_t>(out.steps.size()) - 1;
+    }
+
+    // What form each value is read in.
+    auto need = [&](NodeId v, Rep rep) { out.needs[static_cast<std::size_t>(v)][rep] = true; };
+    for (const Step& s : out.steps) {
+        if (s.kind == Step::Kind::Elementwise) {
+            for (NodeId in : s.inputs) need(in, kRepF32);
+            continue;
+        }
+        const bool half = s.arith == Arith::Bf16 || s.arith == Arith::F16;
+        need(s.lhs, half ? kRepHalf : kRepF32);
+        if (half) {
+            need(s.rhs, s.rhs_transposed ? kRepHalfT : kRepHalf);
+        } else {
+            need(s.rhs, s.rhs_transposed ? kRepF32T : kRepF32);
+        }
+        if (s.has_epilogue) {
+            for (std::size_t k = 0; k < s.inputs.size(); ++k) {
+                if (!s.load_is_accumulator[k]) need(s.inputs[k], kRepF32);
+            }
+        }
+    }
+    for (NodeId o : graph.outputs()) need(o, kRepF32);
+
+    // Derived forms that no kernel writes directly come from the FP32 form by a recast.
+    out.after_step.resize(out.steps.size());
+    for (std::size_t i = 0; i < count; ++i) {
+        const auto id = static_cast<NodeId>(i);
+        const Node& n = graph.node(id);
+        auto& needs = out.needs[i];
+        if (is_compute(n.op)) {
+            if (step_of[i] < 0) continue;  // a folded matmul has no value of its own
+            for (Rep rep : {kRepHalfT, kRepF32T}) {
+                if (!needs[rep]) continue;
+                needs[kRepF32] = true;
+                out.after_step[static_cast<std::size_t>(step_of[i])].push_back({id, rep});
+            }
+            if (!needs[kRepF32] && !needs[kRepHalf]) needs[kRepF32] = true;  // a dead node still runs and writes
+        } else {
+            for (Rep rep : {kRepHalf, kRepHalfT, kRepF32T}) {
+                if (!needs[rep]) continue;
+                if (n.op == OpKind::Input) {
+                    out.after_upload.push_back({id, rep});
+                } else {
+                    out.at_compile.push_back({id, rep});
+                }
+            }
+            needs[kRepF32] = true;  // inputs and constants always land in FP32 first
+        }
+    }
+    for (Step& s : out.steps) {
+        const auto& needs = out.needs[static_cast<std::size_t>(s.result)];
+        s.write_f32 = needs[kRepF32];
+        s.write_half = needs[kRepHalf] ? out.half_kind : HalfKind::None;
+    }
+
+    // Launch count and the shared split-K workspace.
+    for (std::size_t i = 0; i < out.steps.size(); ++i) {
+        const Step& s = out.steps[i];
+        out.kernel_launches += static_cast<std::size_t>(s.launches) + out.after_step[i].size();
+        if (s.kind == Step::Kind::Matmul && s.splits > 1) {
+            out.workspace_bytes = std::max(out.workspace_bytes, static_cast<std::size_t>(s.splits) * s.m * s.n * sizeof(float));
+        }
+    }
+
+    // Buffer plan over the forms of every computed value.
+    out.pool_values.assign(count * kNumReps, PoolValue{});
+    for (std::size_t i = 0; i < count; ++i) {
+        const Node& n = graph.node(static_cast<NodeId>(i));
+        for (int rep = 0; rep < kNumReps; ++rep) {
+            PoolValue& v = out.pool_values[i * kNumReps + static_cast<std::size_t>(rep)];
+            v.bytes = rep_bytes(n.type, static_cast<Rep>(rep));
+            v.pooled = is_compute(n.op) && out.needs[i][static_cast<std::size_t>(rep)];
+            v.live_out = rep == kRepF32 && graph.is_output(static_cast<NodeId>(i));
+        }
+    }
+    auto value_index = [](NodeId node, Rep rep) { return static_cast<std::int32_t>(node) * kNumReps + rep; };
+    for (std::size_t i = 0; i < out.steps.size(); ++i) {
+        const Step& s = out.steps[i];
+        PoolStep ps;
+        for (int rep = 0; rep < kNumReps; ++rep) {
+            if (out.needs[static_cast<std::size_t>(s.result)][static_cast<std::size_t>(rep)]) {
+                ps.defines.push_back(value_index(s.result, static_cast<Rep>(rep)));
+            }
+        }
+        if (s.kind == Step::Kind::Elementwise) {
+            for (NodeId in : s.inputs) ps.reads.push_back(value_index(in, kRepF32));
+        } else {
+            const bool half = s.arith == Arith::Bf16 || s.arith == Arith::F16;
+            ps.reads.push_back(value_index(s.lhs, half ? kRepHalf : kRepF32));
+            ps.reads.push_back(value_index(s.rhs, half ? (s.rhs_transposed ? kRepHalfT : kRepHalf)
+                                                       : (s.rhs_transposed ? kRepF32T : kRepF32)));
+            for (std::size_t k = 0; k < s.inputs.size(); ++k) {
+                if (!s.load_is_accumulator[k]) ps.reads.push_back(value_index(s.inputs[k], kRepF32));
+            }
+        }
+        out.pool_steps.push_back(std::move(ps));
+    }
+    out.pool = plan_pool(out.pool_values, out.pool_steps);
+    return out;
+}
+
+// ---------------------------------------------------------------- epilogue
+
+std::string generate_epilogue_source(const Graph& graph, const Step& step) {
+    std::ostringstream os;
+    os << "// Generated by minicompiler-b200: epilogue of matmul '" << graph.node(step.matmul).name << "' computing '"
+       << graph.node(step.result).name << "' (" << step.program.num_ops() << " elementwise op(s)).\n";
+    os << "#define MC_EPILOGUE_DEFINED 1\n";
+    os << "struct McEpilogueArgs {\n    const float* p[6];\n};\n";
+    os << "__device__ __forceinline__ float mc_epilogue(float acc, unsigned row, unsigned col, const McEpilogueArgs& e) {\n";
+    os << "    (void)row;\n    (void)col;\n    (void)e;\n";
+    // Program input k -> slot in McEpilogueArgs::p (accumulator loads take none).
+    std::vector<int> slot(step.inputs.size(), -1);
+    int next = 0;
+    for (std::size_t k = 0; k < step.inputs.size(); ++k) {
+        if (!step.load_is_accumulator[k]) slot[k] = next++;
+    }
+    for (std::size_t r = 0; r < step.program.instrs.size(); ++r) {
+        const FusedInstr& ins = step.program.instrs[r];
+        os << "    const float r" << r << " = ";
+        switch (ins.kind) {
+            case FusedInstr::Kind::Load: {
+                const auto k = static_cast<std::size_t>(ins.a);
+                if (step.load_is_accumulator[k]) {
+                    os << "acc";
+                    break;
+                }
+                const std::string p = "e.p[" + std::to_string(slot[k]) + "]";
+                switch (step.operands[k].kind) {
+                    case EpilogueOperand::Kind::Scalar: os << "__ldg(" << p << ")"; break;
+                    case EpilogueOperand::Kind::Row: os << "__ldg(" << p << " + col)"; break;
+                    case EpilogueOperand::Kind::Column: os << "__ldg(" << p << " + row)"; break;
+                    case EpilogueOperand::Kind::Full:
+                        os << "__ldg(" << p << " + ((unsigned long long)row * " << step.n << "ull + col))";
+                        break;
+                }
+                break;
+            }
+            case FusedInstr::Kind::Immediate: {
+                char note[40];
+                std::snprintf(note, sizeof note, "%.9g", static_cast<double>(ins.immediate));
+                os << float_bits_literal(ins.immediate) << ";  // " << note << "\n";
+                continue;
+            }
+            case FusedInstr::Kind::Unary: os << op_expression(ins.op, "r" + std::to_string(ins.a), ""); break;
+            case FusedInstr::Kind::Binary:
+                os << op_expression(ins.op, "r" + std::to_string(ins.a), "r" + std::to_string(ins.b));
+                break;
+        }
+        os << ";\n";
+    }
+    os << "    return r" << step.program.instrs.size() - 1 << ";\n}\n";
+    return os.str();
+}
+
+std::string describe(const Graph& graph, const LoweredGraph& lowered) {
+    std::ostringstream os;
+    for (std::size_t i = 0; i < lowered.steps.size(); ++i) {
+        const Step& s = lowered.steps[i];
+        os << i << ": ";
+        if (s.kind == Step::Kind::Elementwise) {
+            os << "elementwise " << graph.node(s.result).name << " ops=" << s.program.num_ops();
+        } else {
+            os << "matmul " << graph.node(s.matmul).name << " " << s.m << "x" << s.n << "x" << s.k << " kernel="
+               << matmul_kernel_name(s.kernel) << " splits=" << s.splits;
+            if (s.rhs_transposed) os << " rhs=transposed";
+            if (s.has_epilogue) os << " epilogue=" << graph.node(s.result).name << "(" << s.program.num_ops() << " ops)";
+        }
+        os << " out=" << (s.write_f32 ? "f32" : "") << (s.write_f32 && s.write_half != HalfKind::None ? "+" : "")
+           << (s.write_half == HalfKind::Bf16 ? "bf16" : s.write_half == HalfKind::F16 ? "f16" : "");
+        os << " launches=" << s.launches << "\n";
+        for (const Recast& rc : lowered.after_step[i]) {
+            os << "   recast " << graph.node(rc.node).name << " -> rep " << static_cast<int>(rc.to) << "\n";
+        }
+    }
+    return os.str();
+}
+
+}  // namespace minicompiler::cuda

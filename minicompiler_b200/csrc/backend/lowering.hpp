@@ -1,0 +1,148 @@
+#pragma once
+// Graph -> launch plan for B200. Pure host logic with no CUDA dependency, so it
+// is exercised on machines without a GPU.
+//
+// It keeps the reference's matmul-kernel vocabulary and selection rules
+// (include/minicompiler/cuda/cuda_backend.hpp:20-56, src/cuda/cuda_backend.cpp:14-49,
+// src/cuda/matmul_kernels.cu:352-383) and adds what the reference lists as future
+// work: an elementwise / fused node whose only matmul-shaped operand is a matmul
+// result with no other user is folded into that matmul's epilogue, so the product
+// never goes to memory in FP32 and one launch disappears.
+
+#include "backend/eltwise_codegen.hpp"
+#include "core/ir.hpp"
+#include "core/plan.hpp"
+
+#include <array>
+#include <cstddef>
+#include <string>
+#include <vector>
+
+namespace minicompiler::cuda {
+
+// Names kept from the reference. On B200 the seven FP32 names all run the one
+// FP32 SIMT kernel (SplitK forces the split rule, Auto applies it when the output
+// cannot fill the GPU); the TensorCore* names run the tcgen05 kernels.
+enum class MatmulKernel {
+    Auto,
+    Naive,
+    Tiled,
+    RegisterTiled128,
+    RegisterTiled64,
+    Vectorized,
+    DoubleBuffered,
+    SplitK,
+    TensorCoreTf32,
+    TensorCoreBf16,
+    TensorCoreF16,
+};
+
+const char* matmul_kernel_name(MatmulKernel kernel);
+Result<MatmulKernel> matmul_kernel_from_name(const std::string& name);
+bool is_tensor_core(MatmulKernel kernel);
+bool uses_split_k(MatmulKernel kernel);
+
+// The reference's split rule, from the count of 128x128 output tiles
+// (src/cuda/matmul_kernels.cu:352-367); its tests pin known answers for 30 SMs.
+int split_k_splits(int m, int n, int k, int sm_count, int blocks_per_sm = 2);
+// The rule for the tcgen05 kernels: 128x256 tiles, one persistent CTA per SM.
+int tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes);
+MatmulKernel resolve_matmul_kernel(MatmulKernel kernel, int m, int n, int k, int sm_count);
+int matmul_splits(MatmulKernel kernel, int m, int n, int k, int sm_count);
+std::size_t matmul_workspace_bytes(MatmulKernel kernel, int m, int n, int splits);
+
+// How the B operand of a tensor-core matmul is laid out for the kernel.
+enum class BLayout : int {
+    Auto = 0,       // as stored by the graph ([k,n] row-major, an "MN-major" operand)
+    RowMajorKN = 1, // same, forced
+    Transposed = 2, // a [n,k] copy ("K-major"); free for constants, one pass for inputs
+};
+
+struct CudaOptions {
+    int device = 0;
+    MatmulKernel matmul = MatmulKernel::Auto;
+    bool vectorize = true;
+    // Additions (trailing, defaulted): not part of the reference's struct.
+    bool fuse_epilogue = true;
+    BLayout b_layout = BLayout::Auto;
+    unsigned eltwise_unroll = 4;
+    bool streaming_hints = true;
+    int gemm_variant = 0;
+};
+
+enum class Arith : int { F32 = 0, Tf32 = 1, Bf16 = 2, F16 = 3 };  // same numbering as MCD_GEMM_*
+
+// The forms a value can be held in on the device.
+enum Rep : int { kRepF32 = 0, kRepHalf = 1, kRepHalfT = 2, kRepF32T = 3, kNumReps = 4 };
+
+struct EpilogueOperand {
+    enum class Kind { Scalar, Row, Column, Full };
+    NodeId node = kNoNode;
+    Kind kind = Kind::Full;
+};
+
+struct Step {
+    enum class Kind { Elementwise, Matmul };
+    Kind kind = Kind::Elementwise;
+    NodeId result = kNoNode;  // the node whose value this step defines
+
+    // Elementwise: `program` over `inputs`. Matmul with a folded consumer: `program` is the
+    // consumer's program, loads of `matmul` read the accumulator, other loads read `operands`.
+    FusedProgram program;
+    std::vector<NodeId> inputs;
+
+    NodeId matmul = kNoNode;
+    NodeId lhs = kNoNode;
+    NodeId rhs = kNoNode;
+    int m = 0, n = 0, k = 0;
+    MatmulKernel kernel = MatmulKernel::DoubleBuffered;  // what matmul_kernels() reports
+    Arith arith = Arith::F32;
+    int splits = 1;
+    bool rhs_transposed = false;
+    bool has_epilogue = false;
+    std::vector<EpilogueOperand> operands;  // indexed by the program's load numbers (entry for the matmul unused)
+    std::vector<int> load_is_accumulator;   // per program input: 1 when it is the matmul result
+
+    bool write_f32 = true;
+    HalfKind write_half = HalfKind::None;
+    int launches = 1;
+};
+
+// A copy made right after a step (or right after upload, for inputs): f32 -> another Rep.
+struct Recast {
+    NodeId node = kNoNode;
+    Rep to = kRepHalf;
+};
+
+struct LoweredGraph {
+    std::vector<Step> steps;
+    std::vector<std::vector<Recast>> after_step;  // per step
+    std::vector<Recast> after_upload;             // for graph inputs
+    std::vector<Recast> at_compile;               // for constants
+    // needs[node][rep]: that form of the value is read by some step (or is a graph output).
+    std::vector<std::array<bool, kNumReps>> needs;
+    HalfKind half_kind = HalfKind::None;
+    std::size_t kernel_launches = 0;
+
+    // Buffer plan over (node, rep) values: index node * kNumReps + rep.
+    std::vector<PoolValue> pool_values;
+    std::vector<PoolStep> pool_steps;
+    PoolPlan pool;
+    std::size_t workspace_bytes = 0;  // one split-K workspace shared by all steps
+};
+
+// Row pitch (in elements) of the 16-bit copy of a rank-2 tensor with `cols` columns:
+// padded so that every row starts on a 16-byte boundary, as TMA requires.
+inline std::int64_t half_pitch(std::int64_t cols) { return (cols + 7) / 8 * 8; }
+std::size_t rep_bytes(const TensorType& type, Rep rep);
+
+Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options, int sm_count);
+
+// The `mc_epilogue` device function for a matmul step with a folded consumer
+// (the text that goes in front of mcd_gemm_source()).
+std::string generate_epilogue_source(const Graph& graph, const Step& step);
+
+// One line per step, for tests and `mcc --print-plan`.
+std::string describe(const Graph& graph, const LoweredGraph& lowered);
+
+}  // namespace minicompiler::cuda

@@ -1,0 +1,180 @@
+// FP32 SIMT matmul, the exact path: C[m,n] = epilogue(A[m,k] * B[k,n]) with FP32
+// FMA accumulation, any m, n, k. It stands where the reference's FP32 ladder and
+// its split-K variant stood (src/cuda/matmul_kernels.cu:244-288, :292-315).
+//
+// One 256-thread block owns a 128x128 tile of C and walks K in steps of 16.
+// A is staged transposed (k-major) so that both operands are read from shared
+// memory as 128-bit vectors; each thread keeps an 8x8 block of accumulators laid
+// out as 2x2 quads of 4x4, and the next K step's global loads are in registers
+// while the current one is multiplied. With gridDim.z > 1 each z-slice covers
+// `k_per_split` of K and writes raw partial sums to `workspace[z][m][n]`; the
+// reduction kernel adds them in slice order and applies the epilogue, so the
+// result never depends on block scheduling.
+
+#define MC_F32_BM 128
+#define MC_F32_BN 128
+#define MC_F32_BK 16
+#define MC_F32_APITCH 132
+
+template <bool kVec>
+__device__ __forceinline__ void mc_gemm_f32_body(const float* __restrict__ A, const float* __restrict__ B,
+                                                 float* __restrict__ C, unsigned short* __restrict__ C16, int c16_kind,
+                                                 int M, int N, int K, long long lda, long long ldb, long long ldc,
+                                                 long long ldc16, int k_per_split, float* __restrict__ workspace,
+                                                 const McEpilogueArgs& epi) {
+    __shared__ __align__(16) float As[2][MC_F32_BK][MC_F32_APITCH];
+    __shared__ __align__(16) float Bs[2][MC_F32_BK][MC_F32_BN];
+
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.y * MC_F32_BM;
+    const int n0 = blockIdx.x * MC_F32_BN;
+    const int k_begin = blockIdx.z * k_per_split;
+    const int k_end = min(K, k_begin + k_per_split);
+
+    // Global -> register staging coordinates.
+    const int a_row = tid >> 2;        // 0..63 (and +64)
+    const int a_k = (tid & 3) << 2;    // 0,4,8,12
+    const int b_k = tid >> 5;          // 0..7 (and +8)
+    const int b_n = (tid & 31) << 2;   // 0..124
+
+    float4 a_stage[2];
+    float4 b_stage[2];
+
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = m0 + a_row + h * 64;
+            const int kk = k0 + a_k;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row < M) {
+                const float* src = A + (long long)row * lda + kk;
+                if (kVec && kk + 3 < k_end) {
+                    v = *reinterpret_cast<const float4*>(src);
+                } else {
+                    if (kk + 0 < k_end) v.x = src[0];
+                    if (kk + 1 < k_end) v.y = src[1];
+                    if (kk + 2 < k_end) v.z = src[2];
+                    if (kk + 3 < k_end) v.w = src[3];
+                }
+            }
+            a_stage[h] = v;
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int kk = k0 + b_k + h * 8;
+            const int col = n0 + b_n;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (kk < k_end) {
+                const float* src = B + (long long)kk * ldb + col;
+                if (kVec && col + 3 < N) {
+                    v = *reinterpret_cast<const float4*>(src);
+                } else {
+                    if (col + 0 < N) v.x = src[0];
+                    if (col + 1 < N) v.y = src[1];
+                    if (col + 2 < N) v.z = src[2];
+                    if (col + 3 < N) v.w = src[3];
+                }
+            }
+            b_stage[h] = v;
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = a_row + h * 64;
+            As[buf][a_k + 0][row] = a_stage[h].x;
+            As[buf][a_k + 1][row] = a_stage[h].y;
+            As[buf][a_k + 2][row] = a_stage[h].z;
+            As[buf][a_k + 3][row] = a_stage[h].w;
+            *reinterpret_cast<float4*>(&Bs[buf][b_k + h * 8][b_n]) = b_stage[h];
+        }
+    };
+
+    const int ty = tid >> 4;  // 0..15 -> rows ty*4 and 64 + ty*4
+    const int tx = tid & 15;  // 0..15 -> cols tx*4 and 64 + tx*4
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    }
+
+    const int steps = (k_end - k_begin + MC_F32_BK - 1) / MC_F32_BK;
+    if (steps > 0) {
+        fetch(k_begin);
+        stash(0);
+    }
+    __syncthreads();
+    for (int s = 0; s < steps; ++s) {
+        const int buf = s & 1;
+        if (s + 1 < steps) fetch(k_begin + (s + 1) * MC_F32_BK);
+#pragma unroll
+        for (int kk = 0; kk < MC_F32_BK; ++kk) {
+            const float4 a_lo = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 4]);
+            const float4 a_hi = *reinterpret_cast<const float4*>(&As[buf][kk][64 + ty * 4]);
+            const float4 b_lo = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
+            const float4 b_hi = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
+            const float a[8] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
+            const float b[8] = {b_lo.x, b_lo.y, b_lo.z, b_lo.w, b_hi.x, b_hi.y, b_hi.z, b_hi.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+            }
+        }
+        if (s + 1 < steps) stash(buf ^ 1);
+        __syncthreads();
+    }
+
+    const bool partial = gridDim.z > 1;
+    float* dst = partial ? workspace + (long long)blockIdx.z * M * N : C;
+    const long long ld = partial ? (long long)N : ldc;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int row = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+        if (row >= M) continue;
+#pragma unroll
+        for (int jh = 0; jh < 2; ++jh) {
+            const int col = n0 + jh * 64 + tx * 4;
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[j] = acc[i][jh * 4 + j];
+                if (!partial && col + j < N) v[j] = mc_epilogue(v[j], (unsigned)row, (unsigned)(col + j), epi);
+            }
+            if (dst != nullptr) {
+                float* out = dst + (long long)row * ld + col;
+                if (kVec && col + 3 < N && (ld & 3) == 0) {
+                    *reinterpret_cast<float4*>(out) = make_float4(v[0], v[1], v[2], v[3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (col + j < N) out[j] = v[j];
+                    }
+                }
+            }
+            if (!partial && C16 != nullptr) {
+                unsigned short* out16 = C16 + (long long)row * ldc16 + col;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (col + j < N) out16[j] = mc_to_half(v[j], c16_kind);
+                }
+            }
+        }
+    }
+}
+
+// kVec: A, B, C (and the workspace) are 16-byte aligned and lda, ldb are multiples of 4.
+extern "C" __global__ void __launch_bounds__(256, 2)
+mc_gemm_f32_vec(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
+                unsigned short* __restrict__ C16, int c16_kind, int M, int N, int K, long long lda, long long ldb,
+                long long ldc, long long ldc16, int k_per_split, float* __restrict__ workspace, McEpilogueArgs epi) {
+    mc_gemm_f32_body<true>(A, B, C, C16, c16_kind, M, N, K, lda, ldb, ldc, ldc16, k_per_split, workspace, epi);
+}
+
+extern "C" __global__ void __launch_bounds__(256, 2)
+mc_gemm_f32_any(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
+                unsigned short* __restrict__ C16, int c16_kind, int M, int N, int K, long long lda, long long ldb,
+                long long ldc, long long ldc16, int k_per_split, float* __restrict__ workspace, McEpilogueArgs epi) {
+    mc_gemm_f32_body<false>(A, B, C, C16, c16_kind, M, N, K, lda, ldb, ldc, ldc16, k_per_split, workspace, epi);
+}

@@ -1,0 +1,394 @@
+// Device layer, part 2: the ahead-of-time compiled kernels (identity epilogue)
+// and the host launchers behind mcd_gemm / mcd_cast_f32_to_half / mcd_transpose_f32.
+// The kernel bodies live in the .cuh files next to this one; the very same text
+// is embedded in the library (mcd_gemm_source) so that a fused epilogue can be
+// compiled in front of it at run time.
+
+#include "minicompiler_b200_device.h"
+
+#include "device/driver_api.hpp"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cstdint>
+#include <cstring>
+#include <string>
+
+#include "kernels/epilogue.cuh"
+#include "kernels/gemm_f32_simt.cuh"
+#include "kernels/gemm_tcgen05.cuh"
+#include "kernels/splitk_reduce.cuh"
+
+namespace mcd {
+extern std::atomic<unsigned long long> g_launches;
+extern const char* const kSourceEpilogue;
+extern const char* const kSourceGemmF32;
+extern const char* const kSourceGemmTc;
+extern const char* const kSourceSplitkReduce;
+}  // namespace mcd
+
+using namespace mcd;
+
+// --------------------------------------------------------------- cast kernels
+
+namespace {
+
+// One 32x32 tile per block through shared memory, so both the read and the
+// (possibly transposed) write are coalesced.
+template <typename Out, bool kTranspose>
+__global__ void __launch_bounds__(256) mc_cast_tile(const float* __restrict__ src, Out* __restrict__ dst, long long rows,
+                                                    long long cols, long long src_pitch, long long dst_pitch, int kind) {
+    __shared__ float tile[32][33];
+    const long long tiles_c = (cols + 31) / 32;
+    const long long tiles_r = (rows + 31) / 32;
+    const int tx = threadIdx.x & 31;
+    const int ty = threadIdx.x >> 5;  // 0..7
+    for (long long t = blockIdx.x; t < tiles_r * tiles_c; t += gridDim.x) {
+        const long long r0 = (t / tiles_c) * 32;
+        const long long c0 = (t % tiles_c) * 32;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const long long r = r0 + ty + 8 * i;
+            const long long c = c0 + tx;
+            tile[ty + 8 * i][tx] = (r < rows && c < cols) ? src[r * src_pitch + c] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (kTranspose) {
+                const long long c = c0 + ty + 8 * i;  // becomes the row of dst
+                const long long r = r0 + tx;
+                if (c < cols && r < rows) {
+                    const float v = tile[tx][ty + 8 * i];
+                    if constexpr (sizeof(Out) == 2) {
+                        dst[c * dst_pitch + r] = mc_to_half(v, kind);
+                    } else {
+                        dst[c * dst_pitch + r] = v;
+                    }
+                }
+            } else {
+                const long long r = r0 + ty + 8 * i;
+                const long long c = c0 + tx;
+                if (r < rows && c < cols) {
+                    const float v = tile[ty + 8 * i][tx];
+                    if constexpr (sizeof(Out) == 2) {
+                        dst[r * dst_pitch + c] = mc_to_half(v, kind);
+                    } else {
+                        dst[r * dst_pitch + c] = v;
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// Dense, 8-aligned rows: 8 floats in, one 16-byte store out per thread-iteration.
+__global__ void __launch_bounds__(256) mc_cast_rows_vec8(const float* __restrict__ src, unsigned short* __restrict__ dst,
+                                                         long long rows, long long cols, long long src_pitch,
+                                                         long long dst_pitch, int kind) {
+    const long long groups_per_row = cols >> 3;
+    const long long groups = rows * groups_per_row;
+    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += (long long)gridDim.x * blockDim.x) {
+        const long long r = g / groups_per_row;
+        const long long c = (g % groups_per_row) << 3;
+        const float4 lo = __ldcs(reinterpret_cast<const float4*>(src + r * src_pitch + c));
+        const float4 hi = __ldcs(reinterpret_cast<const float4*>(src + r * src_pitch + c + 4));
+        uint4 pack;
+        pack.x = mc_to_half2(lo.x, lo.y, kind);
+        pack.y = mc_to_half2(lo.z, lo.w, kind);
+        pack.z = mc_to_half2(hi.x, hi.y, kind);
+        pack.w = mc_to_half2(hi.z, hi.w, kind);
+        *reinterpret_cast<uint4*>(dst + r * dst_pitch + c) = pack;
+    }
+}
+
+int sm_count_of_current_device() {
+    static int cached[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+    int sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+    if (dev >= 0 && dev < 64) cached[dev] = sms;
+    return sms;
+}
+
+int launched(const char* what) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return check_rt(cudaGetLastError(), what);
+}
+
+}  // namespace
+
+extern "C" int mcd_cast_f32_to_half(int half_kind, const float* src, void* dst, long long rows, long long cols,
+                                    long long src_pitch, long long dst_pitch, int transpose, void* stream) {
+    if (half_kind != MCD_HALF_BF16 && half_kind != MCD_HALF_F16) return fail("mcd_cast_f32_to_half: unknown 16-bit format");
+    if (rows <= 0 || cols <= 0) return 0;
+    auto s = static_cast<cudaStream_t>(stream);
+    auto* out = static_cast<unsigned short*>(dst);
+    const int sms = sm_count_of_current_device();
+    const bool vec = !transpose && cols % 8 == 0 && src_pitch % 4 == 0 && dst_pitch % 8 == 0 &&
+                     (reinterpret_cast<std::uintptr_t>(src) & 15) == 0 && (reinterpret_cast<std::uintptr_t>(dst) & 15) == 0;
+    if (vec) {
+        const long long groups = rows * (cols / 8);
+        const unsigned grid = static_cast<unsigned>(std::min<long long>((groups + 255) / 256, 8LL * sms));
+        mc_cast_rows_vec8<<<grid, 256, 0, s>>>(src, out, rows, cols, src_pitch, dst_pitch, half_kind);
+        return launched("mc_cast_rows_vec8");
+    }
+    const long long tiles = ((rows + 31) / 32) * ((cols + 31) / 32);
+    const unsigned grid = static_cast<unsigned>(std::min<long long>(tiles, 16LL * sms));
+    if (transpose) {
+        mc_cast_tile<unsigned short, true><<<grid, 256, 0, s>>>(src, out, rows, cols, src_pitch, dst_pitch, half_kind);
+    } else {
+        mc_cast_tile<unsigned short, false><<<grid, 256, 0, s>>>(src, out, rows, cols, src_pitch, dst_pitch, half_kind);
+    }
+    return launched("mc_cast_tile");
+}
+
+extern "C" int mcd_transpose_f32(const float* src, float* dst, long long rows, long long cols, long long src_pitch,
+                                 long long dst_pitch, void* stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    const long long tiles = ((rows + 31) / 32) * ((cols + 31) / 32);
+    const unsigned grid = static_cast<unsigned>(std::min<long long>(tiles, 16LL * sm_count_of_current_device()));
+    mc_cast_tile<float, true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(src, dst, rows, cols, src_pitch, dst_pitch, 0);
+    return launched("mc_cast_tile<float>");
+}
+
+// ------------------------------------------------------------------ matmuls
+
+namespace {
+
+McEpilogueArgs epilogue_args(const mcd_gemm_args* a) {
+    McEpilogueArgs e;
+    for (int i = 0; i < 6; ++i) e.p[i] = i < a->num_epilogue_inputs ? a->epilogue_inputs[i] : nullptr;
+    return e;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<std::uintptr_t>(p) & 15) == 0; }
+
+int reduce_splits(const mcd_gemm_args* a, int splits, cudaStream_t s) {
+    McEpilogueArgs epi = epilogue_args(a);
+    const long long count = static_cast<long long>(a->m) * a->n;
+    const long long items = (a->n % 4 == 0) ? count / 4 : count;
+    const unsigned grid = static_cast<unsigned>(
+        std::max<long long>(1, std::min<long long>((items + 255) / 256, 8LL * sm_count_of_current_device())));
+    const float* ws = a->workspace;
+    float* c = a->c;
+    auto* c16 = static_cast<unsigned short*>(a->c16);
+    int kind = a->c16_kind, m = a->m, n = a->n;
+    long long ldc = a->ldc, ldc16 = a->ldc16;
+    if (a->reduce_function != nullptr) {
+        void* params[] = {&ws, &c, &c16, &kind, &m, &n, &ldc, &ldc16, &splits, &epi};
+        return mcd_launch(a->reduce_function, grid, 1, 1, 256, 0, s, params);
+    }
+    mc_splitk_reduce<<<grid, 256, 0, s>>>(ws, c, c16, kind, m, n, ldc, ldc16, splits, epi);
+    return launched("mc_splitk_reduce");
+}
+
+int gemm_f32(const mcd_gemm_args* a, cudaStream_t s) {
+    if (a->b_transposed) return fail("mcd_gemm: the FP32 kernel reads B as [k,n]");
+    const int kstep = MC_F32_BK;
+    int splits = std::max(1, a->splits);
+    int k_per_split = ((a->k + splits - 1) / splits + kstep - 1) / kstep * kstep;
+    splits = (a->k + k_per_split - 1) / k_per_split;
+    if (splits > 1 && a->workspace == nullptr) return fail("mcd_gemm: a split matmul needs a workspace");
+    const bool vec = aligned16(a->a) && aligned16(a->b) && (a->c == nullptr || aligned16(a->c)) && a->lda % 4 == 0 &&
+                     a->ldb % 4 == 0 && (splits == 1 || aligned16(a->workspace));
+    const dim3 grid((a->n + MC_F32_BN - 1) / MC_F32_BN, (a->m + MC_F32_BM - 1) / MC_F32_BM, splits);
+    McEpilogueArgs epi = epilogue_args(a);
+    const auto* pa = static_cast<const float*>(a->a);
+    const auto* pb = static_cast<const float*>(a->b);
+    float* pc = a->c;
+    auto* pc16 = static_cast<unsigned short*>(a->c16);
+    int kind = a->c16_kind, m = a->m, n = a->n, k = a->k;
+    long long lda = a->lda, ldb = a->ldb, ldc = a->ldc, ldc16 = a->ldc16;
+    float* ws = a->workspace;
+    if (a->function != nullptr && splits == 1) {
+        // `function` is the entry point mcd_gemm_entry_point named for these arguments.
+        void* params[] = {&pa, &pb, &pc, &pc16, &kind, &m, &n, &k, &lda, &ldb, &ldc, &ldc16, &k_per_split, &ws, &epi};
+        return mcd_launch(a->function, grid.x, grid.y, grid.z, 256, 0, s, params);
+    }
+    if (vec) {
+        mc_gemm_f32_vec<<<grid, 256, 0, s>>>(pa, pb, pc, pc16, kind, m, n, k, lda, ldb, ldc, ldc16, k_per_split, ws, epi);
+    } else {
+        mc_gemm_f32_any<<<grid, 256, 0, s>>>(pa, pb, pc, pc16, kind, m, n, k, lda, ldb, ldc, ldc16, k_per_split, ws, epi);
+    }
+    if (int rc = launched("mc_gemm_f32")) return rc;
+    if (splits > 1) return reduce_splits(a, splits, s);
+    return 0;
+}
+
+unsigned instruction_descriptor(int arith, bool b_is_k_major) {
+    // c_format F32 (1) at bit 4; a/b formats at bits 7 and 10 (F16 0, BF16 1, TF32 2);
+    // b_major at bit 16 (1 = MN-major); N >> 3 at bit 17; M >> 4 at bit 24.
+    const unsigned fmt = arith == MCD_GEMM_F16 ? 0u : arith == MCD_GEMM_BF16 ? 1u : 2u;
+    unsigned d = 0;
+    d |= 1u << 4;
+    d |= fmt << 7;
+    d |= fmt << 10;
+    d |= (b_is_k_major ? 0u : 1u) << 16;
+    d |= static_cast<unsigned>(MC_TC_BN >> 3) << 17;
+    d |= static_cast<unsigned>(MC_TC_BM >> 4) << 24;
+    return d;
+}
+
+int encode_map(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, unsigned long long inner,
+               unsigned long long outer, unsigned long long pitch_elems, unsigned box_inner, unsigned box_outer) {
+    const DriverApi* drv = driver_api();
+    if (drv == nullptr) return fail("the CUDA driver API is unavailable");
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {pitch_elems * static_cast<unsigned long long>(elem_bytes)};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    return check_drv(drv->TensorMapEncodeTiled(map, type, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+                     "cuTensorMapEncodeTiled");
+}
+
+int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
+    const bool tf32 = a->arith == MCD_GEMM_TF32;
+    const int elem = tf32 ? 4 : 2;
+    const int block_k = 128 / elem;
+    const bool b_k_major = a->b_transposed != 0;
+    if (!aligned16(a->a) || !aligned16(a->b) || (a->lda * elem) % 16 != 0 || (a->ldb * elem) % 16 != 0) {
+        return fail("mcd_gemm: tensor-core operands need 16-byte aligned bases and row pitches");
+    }
+    const int k_blocks = (a->k + block_k - 1) / block_k;
+    int splits = std::max(1, std::min(a->splits, k_blocks));
+    const int per = (k_blocks + splits - 1) / splits;
+    splits = (k_blocks + per - 1) / per;
+    if (splits > 1 && a->workspace == nullptr) return fail("mcd_gemm: a split matmul needs a workspace");
+
+    CUtensorMapDataType type = tf32 ? ((a->variant & 1) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_TFLOAT32)
+                               : a->arith == MCD_GEMM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    McTensorMap map_a, map_b;
+    static_assert(sizeof(McTensorMap) == sizeof(CUtensorMap), "tensor map size");
+    if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_a), type, elem, a->a, a->k, a->m, a->lda, block_k, MC_TC_BM)) {
+        return rc;
+    }
+    if (b_k_major) {
+        if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_b), type, elem, a->b, a->k, a->n, a->ldb, block_k, MC_TC_BN)) {
+            return rc;
+        }
+    } else {
+        if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_b), type, elem, a->b, a->n, a->k, a->ldb, 128 / elem, block_k)) {
+            return rc;
+        }
+    }
+
+    McTcParams p;
+    p.c = a->c;
+    p.c16 = static_cast<unsigned short*>(a->c16);
+    p.workspace = a->workspace;
+    p.status = a->status;
+    p.ldc = a->ldc;
+    p.ldc16 = a->ldc16;
+    p.c16_kind = a->c16_kind;
+    p.m = a->m;
+    p.n = a->n;
+    p.k = a->k;
+    p.idesc = instruction_descriptor(a->arith, b_k_major);
+    p.k_blocks_per_split = per;
+    p.splits = splits;
+    McEpilogueArgs epi = epilogue_args(a);
+
+    const int tiles = ((a->m + MC_TC_BM - 1) / MC_TC_BM) * ((a->n + MC_TC_BN - 1) / MC_TC_BN) * splits;
+    const unsigned grid = static_cast<unsigned>(std::max(1, std::min(tiles, sm_count_of_current_device())));
+
+    if (a->function != nullptr && splits == 1) {
+        void* params[] = {&map_a, &map_b, &p, &epi};
+        return mcd_launch(a->function, grid, 1, 1, MC_TC_THREADS, MC_TC_SMEM_BYTES, s, params);
+    }
+    using Kernel = void (*)(const McTensorMap, const McTensorMap, const McTcParams, const McEpilogueArgs);
+    Kernel kernel = tf32 ? (b_k_major ? mc_gemm_tc_tf32_bk : mc_gemm_tc_tf32_bmn)
+                         : (b_k_major ? mc_gemm_tc_h16_bk : mc_gemm_tc_h16_bmn);
+    static std::atomic<int> configured{0};
+    if (configured.load() != 0xF) {
+        for (Kernel kfn : {mc_gemm_tc_tf32_bk, mc_gemm_tc_tf32_bmn, mc_gemm_tc_h16_bk, mc_gemm_tc_h16_bmn}) {
+            if (int rc = check_rt(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_TC_SMEM_BYTES),
+                                  "cudaFuncSetAttribute(max dynamic shared memory)")) {
+                return rc;
+            }
+        }
+        configured.store(0xF);
+    }
+    kernel<<<grid, MC_TC_THREADS, MC_TC_SMEM_BYTES, s>>>(map_a, map_b, p, epi);
+    if (int rc = launched("mc_gemm_tc")) return rc;
+    if (splits > 1) return reduce_splits(a, splits, s);
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int mcd_gemm(const mcd_gemm_args* args, void* stream) {
+    if (args == nullptr) return fail("mcd_gemm: null arguments");
+    if (args->m <= 0 || args->n <= 0 || args->k <= 0) return fail("mcd_gemm: empty problem");
+    if (args->c == nullptr && args->c16 == nullptr) return fail("mcd_gemm: no output buffer");
+    if (args->num_epilogue_inputs < 0 || args->num_epilogue_inputs > MCD_MAX_EPILOGUE_INPUTS) {
+        return fail("mcd_gemm: too many epilogue inputs");
+    }
+    auto s = static_cast<cudaStream_t>(stream);
+    switch (args->arith) {
+        case MCD_GEMM_F32: return gemm_f32(args, s);
+        case MCD_GEMM_TF32:
+        case MCD_GEMM_BF16:
+        case MCD_GEMM_F16: return gemm_tc(args, s);
+        default: return fail("mcd_gemm: unknown arithmetic");
+    }
+}
+
+extern "C" int mcd_gemm_launches(const mcd_gemm_args* a) {
+    if (a->arith == MCD_GEMM_F32) {
+        int splits = std::max(1, a->splits);
+        const int k_per_split = ((a->k + splits - 1) / splits + MC_F32_BK - 1) / MC_F32_BK * MC_F32_BK;
+        splits = (a->k + k_per_split - 1) / k_per_split;
+        return splits > 1 ? 2 : 1;
+    }
+    const int block_k = a->arith == MCD_GEMM_TF32 ? 32 : 64;
+    const int k_blocks = (a->k + block_k - 1) / block_k;
+    int splits = std::max(1, std::min(a->splits, k_blocks));
+    const int per = (k_blocks + splits - 1) / splits;
+    splits = (k_blocks + per - 1) / per;
+    return splits > 1 ? 2 : 1;
+}
+
+extern "C" const char* mcd_gemm_source(int arith) {
+    static const std::string f32 = std::string(kSourceEpilogue) + kSourceGemmF32;
+    static const std::string tc = std::string(kSourceEpilogue) + kSourceGemmTc;
+    static const std::string reduce = std::string(kSourceEpilogue) + kSourceSplitkReduce;
+    if (arith == MCD_GEMM_F32) return f32.c_str();
+    if (arith < 0) return reduce.c_str();
+    return tc.c_str();
+}
+
+extern "C" const char* mcd_gemm_entry_point(const mcd_gemm_args* a) {
+    if (a == nullptr) return "mc_splitk_reduce";
+    if (a->arith == MCD_GEMM_F32) {
+        const bool vec = aligned16(a->a) && aligned16(a->b) && (a->c == nullptr || aligned16(a->c)) && a->lda % 4 == 0 &&
+                         a->ldb % 4 == 0;
+        return vec ? "mc_gemm_f32_vec" : "mc_gemm_f32_any";
+    }
+    if (a->arith == MCD_GEMM_TF32) return a->b_transposed ? "mc_gemm_tc_tf32_bk" : "mc_gemm_tc_tf32_bmn";
+    return a->b_transposed ? "mc_gemm_tc_h16_bk" : "mc_gemm_tc_h16_bmn";
+}
+
+extern "C" size_t mcd_gemm_dynamic_smem(int arith) {
+    return (arith == MCD_GEMM_TF32 || arith == MCD_GEMM_BF16 || arith == MCD_GEMM_F16) ? MC_TC_SMEM_BYTES : 0;
+}
+
+extern "C" int mcd_tensor_core_supported(int device, int arith) {
+    (void)arith;
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return major == 10 ? 1 : 0;
+}

@@ -1,0 +1,452 @@
+// Tensor-core matmul for sm_100a: C[m,n] = epilogue(A[m,k] * B[k,n]) with BF16,
+// FP16 or TF32 multiplicands and FP32 accumulation. It stands where the
+// reference's WMMA kernel stood (src/cuda/matmul_tensor_core.cu:96-222) and is
+// built on the Blackwell execution model instead:
+//
+//   * one persistent CTA per SM walks (m-block, n-block, k-split) work items in
+//     an order that keeps a wave of CTAs on a near-square patch of C, so A and B
+//     tiles are shared through L2;
+//   * warp 0 (one lane) is the TMA producer: per K block it brings a 128 x 128B
+//     A tile and a 256-column B tile into 128B-swizzled shared memory through a
+//     4-stage mbarrier ring (TMA zero-fills the ragged edges of M, N and K);
+//   * warp 1 (one lane) issues tcgen05.mma (128 x 256 x 16 for 16-bit operands,
+//     128 x 256 x 8 for TF32) from shared-memory descriptors into a TMEM
+//     accumulator and releases each stage with tcgen05.commit;
+//   * warps 2-5 drain the accumulator with tcgen05.ld (each warp owns 32 TMEM
+//     lanes = 32 rows), apply the fused epilogue and store C as FP32 and/or as a
+//     16-bit copy for a downstream tensor-core matmul. TMEM holds two 256-column
+//     accumulators, so the epilogue of one tile overlaps the main loop of the next.
+//
+// B is read either as stored by the graph ([k,n] row-major: "MN-major" operand,
+// mc_gemm_tc_*_bmn) or from a [n,k] copy ("K-major", mc_gemm_tc_*_bk).
+//
+// Every wait is bounded: a wait that exceeds MC_TC_WAIT_NS of wall time records
+// MC_TC_ERR_* in *status, raises a CTA-wide abort flag and every role leaves its
+// loop; the CTA then waits (bounded) for its TMA copies in flight, frees its
+// TMEM and returns.
+
+#define MC_TC_BM 128
+#define MC_TC_BN 256
+#define MC_TC_STAGES 4
+#define MC_TC_THREADS 192
+#define MC_TC_A_BYTES (MC_TC_BM * 128)
+#define MC_TC_B_BYTES (MC_TC_BN * 128)
+#define MC_TC_STAGE_BYTES (MC_TC_A_BYTES + MC_TC_B_BYTES)
+#define MC_TC_SMEM_BYTES (MC_TC_STAGES * MC_TC_STAGE_BYTES + 1024 + 256)
+#define MC_TC_WAIT_NS 2000000000ull
+#define MC_TC_RASTER 16
+
+#define MC_TC_ERR_PRODUCER 0x1u
+#define MC_TC_ERR_MMA 0x2u
+#define MC_TC_ERR_EPILOGUE 0x4u
+#define MC_TC_ERR_DRAIN 0x8u
+
+struct __align__(64) McTensorMap {
+    unsigned long long opaque[16];
+};
+
+struct McTcParams {
+    float* c;
+    unsigned short* c16;
+    float* workspace;
+    unsigned* status;
+    long long ldc;
+    long long ldc16;
+    int c16_kind;
+    int m, n, k;
+    unsigned idesc;
+    int k_blocks_per_split;  // K blocks (of 128 bytes) per work item
+    int splits;
+};
+
+__device__ __forceinline__ unsigned mc_smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long mc_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mc_mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mc_mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mc_mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mc_mbar_try_wait(unsigned bar, unsigned parity) {
+    unsigned done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded wait. Returns false when it gave up (or when another role already did).
+__device__ __forceinline__ bool mc_mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, unsigned* status,
+                                             unsigned err_code) {
+    if (mc_mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = mc_globaltimer();
+    unsigned spins = 0;
+    while (!mc_mbar_try_wait(bar, parity)) {
+        if ((++spins & 255u) == 0u) {
+            if (*abort_flag != 0) return false;
+            if (mc_globaltimer() - t0 > MC_TC_WAIT_NS) {
+                if (status != nullptr) atomicOr(status, err_code);
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void mc_tma_load_2d(unsigned smem_dst, const McTensorMap* map, unsigned bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void mc_umma(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b,
+                                        unsigned idesc, unsigned accumulate, bool tf32) {
+    if (tf32) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+            "}\n" ::"r"(tmem_d),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+            "}\n" ::"r"(tmem_d),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+__device__ __forceinline__ void mc_umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mc_tmem_load32(unsigned taddr, unsigned (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+// Shared-memory operand descriptor, 128-byte swizzle (layout type 2, descriptor version 1).
+__device__ __forceinline__ unsigned long long mc_smem_desc(unsigned addr, unsigned leading_bytes, unsigned stride_bytes) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)((leading_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (unsigned long long)((stride_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+// Work item -> (m block, n block, k split), rastered in bands of MC_TC_RASTER m-blocks.
+__device__ __forceinline__ void mc_tc_decode(int item, int tiles_m, int tiles_n, int splits, int& mb, int& nb, int& split) {
+    split = item % splits;
+    const int tile = item / splits;
+    const int band_tiles = MC_TC_RASTER * tiles_n;
+    const int band = tile / band_tiles;
+    const int first_m = band * MC_TC_RASTER;
+    const int band_rows = min(MC_TC_RASTER, tiles_m - first_m);
+    const int within = tile - band * band_tiles;
+    mb = first_m + within % band_rows;
+    nb = within / band_rows;
+}
+
+template <int kElemBytes, bool kBIsKMajor>
+__device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const McTensorMap& map_b, const McTcParams& p,
+                                                const McEpilogueArgs& epi) {
+    constexpr int kBlockK = 128 / kElemBytes;    // elements per K block (one 128-byte swizzle row)
+    constexpr int kMmaK = 32 / kElemBytes;       // elements per tcgen05.mma
+    constexpr int kMmasPerBlock = kBlockK / kMmaK;  // 4
+    constexpr int kAtomN = 128 / kElemBytes;     // MN-major B: columns per 128-byte atom
+    constexpr bool kTf32 = kElemBytes == 4;
+
+    extern __shared__ unsigned char mc_tc_smem_raw[];
+    const unsigned raw = mc_smem_addr(mc_tc_smem_raw);
+    const unsigned tiles_base = (raw + 1023u) & ~1023u;  // 128B swizzle wants 1024-byte aligned tiles
+    const unsigned bars_base = tiles_base + MC_TC_STAGES * MC_TC_STAGE_BYTES;
+    // barrier slots (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2]
+    const unsigned bar_full = bars_base;
+    const unsigned bar_empty = bars_base + 8 * MC_TC_STAGES;
+    const unsigned bar_tmem_full = bars_base + 16 * MC_TC_STAGES;
+    const unsigned bar_tmem_empty = bar_tmem_full + 16;
+    __shared__ unsigned tmem_base_slot;
+    __shared__ int abort_flag_storage;
+    volatile int* abort_flag = &abort_flag_storage;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int tiles_m = (p.m + MC_TC_BM - 1) / MC_TC_BM;
+    const int tiles_n = (p.n + MC_TC_BN - 1) / MC_TC_BN;
+    const int k_blocks = (p.k + kBlockK - 1) / kBlockK;
+    const int items = tiles_m * tiles_n * p.splits;
+
+    if (threadIdx.x == 0) {
+        abort_flag_storage = 0;
+        for (int s = 0; s < MC_TC_STAGES; ++s) {
+            mc_mbar_init(bar_full + 8 * s, 1);
+            mc_mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mc_mbar_init(bar_tmem_full + 8 * a, 1);
+            mc_mbar_init(bar_tmem_empty + 8 * a, 4);  // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(mc_smem_addr(&tmem_base_slot)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            unsigned phase = 0;
+            int issued = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
+                int mb, nb, split;
+                mc_tc_decode(item, tiles_m, tiles_n, p.splits, mb, nb, split);
+                const int kb_begin = split * p.k_blocks_per_split;
+                const int kb_end = min(k_blocks, kb_begin + p.k_blocks_per_split);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                    ok = mc_mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, MC_TC_ERR_PRODUCER);
+                    if (!ok) break;
+                    const unsigned full = bar_full + 8 * stage;
+                    const unsigned a_dst = tiles_base + stage * MC_TC_STAGE_BYTES;
+                    const unsigned b_dst = a_dst + MC_TC_A_BYTES;
+                    mc_mbar_expect_tx(full, MC_TC_STAGE_BYTES);
+                    mc_tma_load_2d(a_dst, &map_a, full, kb * kBlockK, mb * MC_TC_BM);
+                    if (kBIsKMajor) {
+                        mc_tma_load_2d(b_dst, &map_b, full, kb * kBlockK, nb * MC_TC_BN);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < MC_TC_BN / kAtomN; ++j) {
+                            mc_tma_load_2d(b_dst + j * (kBlockK * 128), &map_b, full, nb * MC_TC_BN + j * kAtomN,
+                                           kb * kBlockK);
+                        }
+                    }
+                    ++issued;
+                    if (++stage == MC_TC_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok) {
+                // Give the copies still in flight time to land before shared memory is released:
+                // the most recently issued min(issued, STAGES) stages each complete their `full` barrier.
+                int s = stage;
+                unsigned ph = phase;
+                const int pending = min(issued, MC_TC_STAGES);
+                for (int i = 0; i < pending; ++i) {
+                    if (s == 0) {
+                        s = MC_TC_STAGES;
+                        ph ^= 1u;
+                    }
+                    --s;
+                    const unsigned long long t0 = mc_globaltimer();
+                    while (!mc_mbar_try_wait(bar_full + 8 * s, ph)) {
+                        if (mc_globaltimer() - t0 > MC_TC_WAIT_NS / 4) {
+                            if (p.status != nullptr) atomicOr(p.status, MC_TC_ERR_DRAIN);
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            int stage = 0;
+            unsigned phase = 0;
+            int acc = 0;
+            unsigned acc_phase = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
+                int mb, nb, split;
+                mc_tc_decode(item, tiles_m, tiles_n, p.splits, mb, nb, split);
+                const int kb_begin = split * p.k_blocks_per_split;
+                const int kb_end = min(k_blocks, kb_begin + p.k_blocks_per_split);
+                ok = mc_mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, MC_TC_ERR_MMA);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned tmem_d = tmem_base + (unsigned)(acc * MC_TC_BN);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                    ok = mc_mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, MC_TC_ERR_MMA);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned a_src = tiles_base + stage * MC_TC_STAGE_BYTES;
+                    const unsigned b_src = a_src + MC_TC_A_BYTES;
+                    // K-major operand: rows of 128 bytes, 8-row groups 1024 bytes apart; a K step is 32 bytes.
+                    const unsigned long long desc_a = mc_smem_desc(a_src, 16, 1024);
+                    // MN-major B: 128-byte atoms of columns, each holding kBlockK rows; 8-row groups 1024 bytes
+                    // apart, atoms kBlockK*128 bytes apart; a K step is kMmaK rows.
+                    const unsigned long long desc_b =
+                        kBIsKMajor ? mc_smem_desc(b_src, 16, 1024) : mc_smem_desc(b_src, kBlockK * 128, 1024);
+                    const unsigned b_step = kBIsKMajor ? 2u : (unsigned)(kMmaK * 128) >> 4;
+#pragma unroll
+                    for (int ks = 0; ks < kMmasPerBlock; ++ks) {
+                        mc_umma(tmem_d, desc_a + (unsigned long long)(2 * ks), desc_b + (unsigned long long)(b_step * ks),
+                                p.idesc, (kb > kb_begin || ks > 0) ? 1u : 0u, kTf32);
+                    }
+                    mc_umma_commit(bar_empty + 8 * stage);  // the stage is free once these MMAs have read it
+                    if (++stage == MC_TC_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                mc_umma_commit(bar_tmem_full + 8 * acc);
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const int quarter = warp & 3;  // the TMEM lanes this warp may touch: [32*quarter, +32)
+        int acc = 0;
+        unsigned acc_phase = 0;
+        bool ok = true;
+        const bool partial = p.splits > 1;
+        for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
+            int mb, nb, split;
+            mc_tc_decode(item, tiles_m, tiles_n, p.splits, mb, nb, split);
+            ok = mc_mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, p.status, MC_TC_ERR_EPILOGUE);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = mb * MC_TC_BM + quarter * 32 + lane;
+            const int n0 = nb * MC_TC_BN;
+            float* dst = partial ? p.workspace + (long long)split * p.m * p.n : p.c;
+            const long long ld = partial ? (long long)p.n : p.ldc;
+            const bool vec4 = (ld & 3) == 0 && (((unsigned long long)dst) & 15) == 0;
+            const bool vec16 = (p.ldc16 & 7) == 0 && (((unsigned long long)p.c16) & 15) == 0;
+#pragma unroll 1
+            for (int chunk = 0; chunk < MC_TC_BN / 32; ++chunk) {
+                const int col0 = n0 + chunk * 32;
+                if (col0 >= p.n) break;  // warp-uniform
+                unsigned v[32];
+                mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * MC_TC_BN + chunk * 32), v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < p.m) {
+                    float f[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        f[j] = __uint_as_float(v[j]);
+                        if (!partial && col0 + j < p.n) f[j] = mc_epilogue(f[j], (unsigned)row, (unsigned)(col0 + j), epi);
+                    }
+                    if (dst != nullptr) {
+                        float* out = dst + (long long)row * ld + col0;
+                        if (vec4 && col0 + 32 <= p.n) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                *reinterpret_cast<float4*>(out + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (col0 + j < p.n) out[j] = f[j];
+                            }
+                        }
+                    }
+                    if (!partial && p.c16 != nullptr) {
+                        unsigned short* out16 = p.c16 + (long long)row * p.ldc16 + col0;
+                        if (vec16 && col0 + 32 <= p.n) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 pack;
+                                pack.x = mc_to_half2(f[j + 0], f[j + 1], p.c16_kind);
+                                pack.y = mc_to_half2(f[j + 2], f[j + 3], p.c16_kind);
+                                pack.z = mc_to_half2(f[j + 4], f[j + 5], p.c16_kind);
+                                pack.w = mc_to_half2(f[j + 6], f[j + 7], p.c16_kind);
+                                *reinterpret_cast<uint4*>(out16 + j) = pack;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (col0 + j < p.n) out16[j] = mc_to_half(f[j], p.c16_kind);
+                            }
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mc_mbar_arrive(bar_tmem_empty + 8 * acc);
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    __syncwarp();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(MC_TC_THREADS, 1)
+mc_gemm_tc_h16_bmn(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
+                   const McTcParams p, const McEpilogueArgs epi) {
+    mc_gemm_tc_body<2, false>(map_a, map_b, p, epi);
+}
+
+extern "C" __global__ void __launch_bounds__(MC_TC_THREADS, 1)
+mc_gemm_tc_h16_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
+                  const McTcParams p, const McEpilogueArgs epi) {
+    mc_gemm_tc_body<2, true>(map_a, map_b, p, epi);
+}
+
+extern "C" __global__ void __launch_bounds__(MC_TC_THREADS, 1)
+mc_gemm_tc_tf32_bmn(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
+                    const McTcParams p, const McEpilogueArgs epi) {
+    mc_gemm_tc_body<4, false>(map_a, map_b, p, epi);
+}
+
+extern "C" __global__ void __launch_bounds__(MC_TC_THREADS, 1)
+mc_gemm_tc_tf32_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
+                   const McTcParams p, const McEpilogueArgs epi) {
+    mc_gemm_tc_body<4, true>(map_a, map_b, p, epi);
+}
