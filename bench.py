@@ -1,0 +1,380 @@
+"""Benchmark of the compiled-graph hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One "step" is one execution of a compiled graph (`mc_enqueue`) on inputs already resident in HBM.
+The default workload is the headline memory-bound config: the tanh-GELU chain on f32[8192,8192]
+(one fused kernel; 536,870,912 algorithmic bytes per step), reported as fused-eltwise HBM GB/s.
+Other workloads (`--workload`): c1, c3_fp32, c3_tf32, c4_bf16, c4_f16, c4_tf32, c4_fp32, c5_f16, c5_bf16
+report graph TFLOP/s. With N > 1 (launched by torchrun, one rank per GPU) c2/c4 run one replica per
+GPU on rank-specific data (weak scaling) and c5/c3/c1 shard their batch dim over the ranks.
+
+Rank 0 prints ONE JSON line. `value` is device-timed with CUDA events on the launching stream,
+max over ranks; `e2e` is the same metric through `mc_run` on pinned host buffers (copies inside
+the timed region); `roofline` relates the dominant kernel to the measured peak in
+MEASURED_PEAKS.json; `cpu_baseline` times the CPU oracle on a bounded sample.
+
+`--impl reference` times the reference's CPU path instead: the Eigen backend cannot be built
+here (Eigen 3.4.0 is not vendored and not installed), so it is the oracle port, on host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+
+# workload -> (graph, dims, matmul kernel, batch dim, metric kind, input distribution)
+WORKLOADS = {
+    "c2": ("c2_gelu_chain", {"M": 8192, "N": 8192}, "auto", None, "bytes", "normal"),
+    "c1": ("c1_mlp_block", {"B": 256}, "auto", "B", "flops", "uniform"),
+    "c3_fp32": ("c3_ffn", {"T": 8192, "D": 1024, "H": 4096}, "auto", "T", "flops", "normal"),
+    "c3_tf32": ("c3_ffn", {"T": 8192, "D": 1024, "H": 4096}, "tensor_core_tf32", "T", "flops", "normal"),
+    "c4_bf16": ("c4_matmul", {"M": 8192, "N": 8192, "K": 8192}, "tensor_core_bf16", None, "flops", "uniform"),
+    "c4_f16": ("c4_matmul", {"M": 8192, "N": 8192, "K": 8192}, "tensor_core_f16", None, "flops", "uniform"),
+    "c4_tf32": ("c4_matmul", {"M": 8192, "N": 8192, "K": 8192}, "tensor_core_tf32", None, "flops", "uniform"),
+    "c4_fp32": ("c4_matmul", {"M": 4096, "N": 4096, "K": 4096}, "auto", None, "flops", "uniform"),
+    "c5_f16": ("c5_mlp_stack", {"B": 65536, "D": 2048}, "tensor_core_f16", "B", "flops", "normal"),
+    "c5_bf16": ("c5_mlp_stack", {"B": 65536, "D": 2048}, "tensor_core_bf16", "B", "flops", "normal"),
+}
+DTYPES = {"auto": "f32", "tensor_core_tf32": "tf32", "tensor_core_bf16": "bf16", "tensor_core_f16": "f16"}
+
+
+def algorithmic_work(oracle, graph, kind):
+    """Bytes: every compute node's output once plus each distinct non-scalar operand once, on the graph as
+    executed (the reference's bytes_moved convention, bench/bench_cuda.cpp:76-95); for the fused GELU chain that
+    is read x + write y. FLOPs: 2 m n k per matmul (bench/bench_cuda.cpp:634)."""
+    if kind == "bytes":
+        x = graph.node(graph.inputs[0])
+        return 2 * 4 * int(np.prod(x.shape))
+    flops = 0
+    for n in graph.nodes:
+        if n.op == "matmul":
+            a, b = graph.node(n.operands[0]), graph.node(n.operands[1])
+            flops += 2 * a.shape[0] * a.shape[1] * b.shape[1]
+    return flops
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples for one GPU while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [t.strip() for t in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs(oracle, graph, dist, seed):
+    ins = []
+    for k, name in enumerate(graph.inputs):
+        shape = graph.node(name).shape
+        n = int(np.prod(shape))
+        v = oracle.normal_values(n, seed + k) if dist == "normal" else oracle.uniform_values(n, seed + k, -1.0, 1.0)
+        ins.append(v.reshape(shape))
+    return ins
+
+
+def cpu_sample_rate(oracle, path, dims, batch_dim, kind, dist, seconds_target=10.0):
+    """Times the CPU oracle (float32, reference CPU-backend semantics) on a row sample of the workload."""
+    sample_dims = dict(dims)
+    lead = batch_dim or ("M" if "M" in dims else None)
+    rows_full = dims[lead] if lead else 1
+    rows = min(rows_full, 512 if kind == "bytes" else 256)
+    if lead:
+        sample_dims[lead] = rows
+    g = oracle.parse_mcg_file(path, sample_dims)
+    ins = make_inputs(oracle, g, dist, 1)
+    oracle.evaluate_f32(g, ins)  # warm
+    t0, reps = time.perf_counter(), 0
+    while True:
+        oracle.evaluate_f32(g, ins)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt > seconds_target or reps >= 50:
+            break
+    work = algorithmic_work(oracle, g, kind)
+    rate = work * reps / dt / (1e9 if kind == "bytes" else 1e12)
+    return rate, f"{rows} of {rows_full} rows of '{lead}', {reps} runs in {dt:.1f} s, numpy float32 (elementwise 1 thread; matmul BLAS)"
+
+
+def run_reference_arm(args):
+    """The reference's CPU path, timed on host cores (rank 0 only)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    from oracle import reference_cpu as oracle
+    import minicompiler_b200 as mc
+
+    name, dims, matmul, batch_dim, kind, dist = WORKLOADS[args.workload]
+    path = mc.graph_path(name)
+    sample_dims = dict(dims)
+    lead = batch_dim or ("M" if "M" in dims else None)
+    rows = min(dims[lead], 256 if kind == "bytes" else 128) if lead else 1
+    if lead:
+        sample_dims[lead] = rows
+    g = oracle.parse_mcg_file(path, sample_dims)
+    ins = make_inputs(oracle, g, dist, 1)
+    work = algorithmic_work(oracle, g, kind)
+    for _ in range(max(1, min(args.warmup, 3))):
+        oracle.evaluate_f32(g, ins)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.evaluate_f32(g, ins)
+    dt = time.perf_counter() - t0
+    unit = "GB/s" if kind == "bytes" else "TFLOP/s"
+    value = work * args.steps / dt / (1e9 if kind == "bytes" else 1e12)
+    cores = os.cpu_count() or 1
+    line = {
+        "impl": "reference", "metric": "fused-eltwise HBM GB/s" if kind == "bytes" else "graph TFLOP/s", "value": value, "unit": unit,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "graph": name, "dims": dims,
+                   "note": "reference CPU path = oracle port (Eigen 3.4.0 is absent, the reference's CPU backend cannot be built); "
+                           f"each step runs a {rows}-row sample of the workload"},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores if kind != "bytes" else 1, "kind": "port",
+                         "sample": f"{rows} rows per step, numpy float32"},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--also", default="", help="comma-separated extra workloads measured briefly (N=1 only)")
+    ap.add_argument("--dims", default="", help="override dims of the workload, e.g. M=4096,N=8192 (for small profiler captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import minicompiler_b200 as mc
+    from oracle import reference_cpu as oracle  # checker / CPU baseline only; never on the measured path
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: no CUDA device is visible and there is no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def measure(workload, steps, warmup, with_e2e, with_cpu):
+        name, dims, matmul, batch_dim, kind, dist_name = WORKLOADS[workload]
+        if args.dims and workload == args.workload:
+            dims = dict(dims) | {k: int(v) for k, v in (kv.split("=") for kv in args.dims.split(","))}
+        path = mc.graph_path(name)
+        my_dims, scaling = dict(dims), "weak"
+        if world > 1 and batch_dim is not None:
+            dims_str, row_offset, rows = mc.shard_dims(path, dims, batch_dim, rank, world)
+            my_dims = {k: int(v) for k, v in (kv.split("=") for kv in dims_str.split(","))}
+            scaling = "strong"
+        exe = mc.CompiledGraph(path, dims=my_dims, options={"device": local_rank, "matmul": matmul})
+        if world > 1:
+            # Constants are generated identically on every rank; one NCCL broadcast over NVLink makes rank 0's
+            # copy the one everybody uses (and is the only collective on this path).
+            ptr, nbytes = exe.constants_region()
+            if nbytes > 0:
+                class _Mem:
+                    __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+                region = torch.as_tensor(_Mem(), device=torch.device("cuda", local_rank))
+                dist.broadcast(region, src=0)
+                torch.cuda.synchronize()
+                exe.refresh_constants()
+        g = oracle.parse_mcg_file(path, my_dims)
+        work_rank = algorithmic_work(oracle, g, kind)
+        ins = make_inputs(oracle, g, dist_name, 1 + 1000 * rank)
+        pinned_in = [torch.from_numpy(a.reshape(-1)).pin_memory() for a in ins]
+        pinned_out = [torch.empty(n, dtype=torch.float32).pin_memory() for n in exe.output_elements]
+        exe.upload([t.numpy() for t in pinned_in])
+        # A stream of our own: torch's default stream has handle 0, which mc_enqueue reads as "the executable's
+        # own stream", and CUDA events only see the stream they are recorded on.
+        stream = torch.cuda.Stream()
+        launches_per_step = exe.kernel_launches
+
+        for _ in range(warmup):
+            exe.enqueue(stream.cuda_stream)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        count0 = mc.lib().mcd_launch_count()
+        events[0].record(stream)
+        for i in range(steps):
+            exe.enqueue(stream.cuda_stream)
+            events[i + 1].record(stream)
+        torch.cuda.synchronize()
+        count1 = mc.lib().mcd_launch_count()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        clocks = sampler.stop() if rank == 0 else None
+        exe.synchronize()  # also surfaces a kernel that gave up a bounded wait
+        total_ms = events[0].elapsed_time(events[-1])
+        per_step = sorted(events[i].elapsed_time(events[i + 1]) for i in range(steps))
+        t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+        w = torch.tensor([float(work_rank)], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(w, op=dist.ReduceOp.SUM)
+        total_ms, work_all = float(t.item()), float(w.item())
+        denom = 1e9 if kind == "bytes" else 1e12
+        value = work_all * steps / (total_ms * 1e-3) / denom
+
+        e2e = None
+        if with_e2e:
+            in_ptrs = [t_.data_ptr() for t_ in pinned_in]
+            out_ptrs = [t_.data_ptr() for t_ in pinned_out]
+            e2e_steps = max(3, min(steps, 10))
+            exe.run_ptrs(in_ptrs, out_ptrs)
+            if world > 1:
+                dist.barrier()
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                exe.run_ptrs(in_ptrs, out_ptrs)  # H2D from pinned memory, kernels, D2H into pinned memory, synchronized
+            dt = time.perf_counter() - t0
+            tt = torch.tensor([dt], dtype=torch.float64, device="cuda")
+            if world > 1:
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            e2e = {"value": work_all * e2e_steps / float(tt.item()) / denom, "unit": "GB/s" if kind == "bytes" else "TFLOP/s",
+                   "h2d_bytes_per_step": int(sum(a.numel() * 4 for a in pinned_in)),
+                   "d2h_bytes_per_step": int(sum(a.numel() * 4 for a in pinned_out)), "steps": e2e_steps,
+                   "timing": "host wall clock around mc_run (it synchronizes), max over ranks"}
+
+        peaks = measured_peaks()
+        median_ms = per_step[len(per_step) // 2]
+        avg_ms = total_ms / steps
+        if kind == "bytes":
+            achieved = work_rank / (avg_ms * 1e-3) / 1e9
+            peak, unit, bound = peaks["hbm_gbs"], "GB/s", "hbm"
+        else:
+            achieved = work_rank / (avg_ms * 1e-3) / 1e12
+            sustained = total_ms > 1000.0
+            base = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
+            peak = {"f32": 2 * 148 * 128 * 1.965e9 / 1e12, "tf32": base / 2.0}.get(DTYPES[matmul], base)
+            unit, bound = "TFLOP/s", "tensor" if matmul != "auto" else "fp32-fma"
+        traffic = None
+        tfile = ROOT / "profiles" / "ncu_traffic.json"
+        if tfile.exists():
+            try:
+                traffic = json.loads(tfile.read_text()).get(workload, {}).get("dram_bytes_per_launch")
+            except Exception:
+                traffic = None
+        roofline = {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                    "traffic": traffic, "peak_source": f"of {peaks['source']}", "kernel_ms_avg": avg_ms, "kernel_ms_median": median_ms,
+                    "algorithmic_per_launch": work_rank}
+
+        cpu = None
+        if with_cpu and rank == 0:
+            rate, sample = cpu_sample_rate(oracle, path, dims, batch_dim, kind, dist_name)
+            cpu = {"value": rate, "unit": "GB/s" if kind == "bytes" else "TFLOP/s", "cores": 1 if kind == "bytes" else (os.cpu_count() or 1),
+                   "kind": "port", "sample": sample}
+
+        result = {
+            "metric": "fused-eltwise HBM GB/s" if kind == "bytes" else "graph TFLOP/s", "value": value,
+            "unit": "GB/s" if kind == "bytes" else "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": avg_ms, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "dtype": DTYPES[matmul], "data": "synthetic",
+            "config": {"workload": workload, "graph": name, "dims": dims, "per_rank_dims": my_dims, "matmul": matmul,
+                       "matmul_kernels": exe.matmul_kernels, "kernel_launches_per_step": launches_per_step,
+                       "l2": "inputs and outputs of a step exceed the 126 MB L2" if work_rank > 3e8 or kind == "flops" else "small",
+                       "inputs": f"{dist_name} (splitmix64 stream, seed 1 + 1000*rank)"},
+            "e2e": e2e, "gpu_launches": int(count1 - count0), "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
+            "jit_compile_ms": exe.jit_compile_ms, "arena_bytes": exe.arena_bytes,
+        }
+        exe.release()
+        return result
+
+    line = measure(args.workload, args.steps, args.warmup, not args.no_e2e, not args.no_cpu_baseline)
+    if args.also and world == 1:
+        extra = []
+        for wl in [w for w in args.also.split(",") if w]:
+            try:
+                r = measure(wl, max(5, min(args.steps, 20)), 3, False, False)
+                extra.append({k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "dtype", "roofline", "gpu_launches")}
+                             | {"workload": wl, "matmul_kernels": r["config"]["matmul_kernels"]})
+            except Exception as e:  # an extra must never lose the headline line
+                extra.append({"workload": wl, "error": str(e)[:300]})
+        line["also"] = extra
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -189,7 +189,9 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
                   : kernel == MatmulKernel::TensorCoreF16  ? Arith::F16
                                                            : Arith::F32;
         s.splits = matmul_splits(kernel, s.m, s.n, s.k, sm_count);
-        s.rhs_transposed = is_tensor_core(kernel) && rhs_transposed;
+        // TF32 always takes the [n,k] copy of B: with 32-bit elements the MN-major shared-memory form did not
+        // yield correct products on B200, while the K-major form does. 16-bit operands work in both forms.
+        s.rhs_transposed = is_tensor_core(kernel) && (rhs_transposed || kernel == MatmulKernel::TensorCoreTf32);
         s.launches = s.splits > 1 ? 2 : 1;
         return s;
     };

@@ -259,6 +259,7 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     if (!aligned16(a->a) || !aligned16(a->b) || (a->lda * elem) % 16 != 0 || (a->ldb * elem) % 16 != 0) {
         return fail("mcd_gemm: tensor-core operands need 16-byte aligned bases and row pitches");
     }
+    if (tf32 && !b_k_major) return fail("mcd_gemm: TF32 reads B as a [n,k] copy only (set b_transposed)");
     const int k_blocks = (a->k + block_k - 1) / block_k;
     int splits = std::max(1, std::min(a->splits, k_blocks));
     const int per = (k_blocks + splits - 1) / splits;

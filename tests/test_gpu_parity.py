@@ -1,0 +1,387 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI, on a B200.
+
+Tolerances are the reference's own between its CUDA and CPU backends
+(tests/test_cuda_backend.cpp:66-72, :119-162, :164-219, :395-437) and the per-precision bars of
+the build target: 1e-5 relative for elementwise FP32 graphs, 1e-4 for FP32 GEMM graphs, 5e-3
+(TF32) and 2e-2 (BF16/FP16) against a norm-scaled FP32 reference.
+"""
+
+import ctypes as C
+import json
+
+import numpy as np
+import pytest
+
+from conftest import GOLDEN
+
+pytestmark = pytest.mark.gpu
+
+U32 = 2.0 ** -24
+
+
+def all_close(actual, expected, rtol, atol):
+    a = np.asarray(actual, dtype=np.float64)
+    e = np.asarray(expected, dtype=np.float64)
+    assert a.shape == e.shape
+    both_nan = np.isnan(a) & np.isnan(e)
+    err = np.abs(a - e)
+    bad = ~(err <= atol + rtol * np.abs(e)) & ~both_nan & ~(a == e)
+    if bad.any():
+        i = int(np.argmax(np.where(bad, err, 0)))
+        return False, f"{int(bad.sum())} of {a.size} elements differ; worst at [{i}]: actual {a[i]!r}, expected {e[i]!r}"
+    return True, ""
+
+
+def run_graph(mc, text=None, path=None, dims=None, passes="default", options=None, inputs=None):
+    with mc.CompiledGraph(path, text=text, dims=dims, passes=passes, options=options or {}) as exe:
+        return exe.run(inputs)
+
+
+def oracle_inputs(oracle, text=None, path=None, dims=None, seed=1, lo=-1.0, hi=1.0):
+    d = None
+    if dims:
+        d = dims if isinstance(dims, dict) else {k: int(v) for k, v in (kv.split("=") for kv in dims.split(","))}
+    g = oracle.parse_mcg(text, d) if text is not None else oracle.parse_mcg_file(path, d)
+    return g, oracle.make_random_inputs(g, seed, lo, hi)
+
+
+# ------------------------------------------------------------- device layer
+
+
+def test_device_is_a_b200_and_reports_sane_peaks(mc):
+    buf = C.create_string_buffer(4096)
+    assert mc.lib().mc_gpu_device_json(None, 0, buf, len(buf)) == 0
+    info = json.loads(buf.value.decode())
+    assert info["compute_capability"].startswith("10.")
+    assert info["sm_count"] >= 100 and info["peak_bandwidth_gbs"] > 1000 and info["peak_fp32_gflops"] > 10000
+
+
+# -------------------------------------------------------------- elementwise
+
+
+@pytest.mark.parametrize("shape", ["[37, 29]", "[64, 64]", "[3, 1000]"])
+def test_unary_ops_match_the_oracle(mc, oracle, shape):
+    # tests/test_cuda_backend.cpp:85-101: exact for neg/relu, rtol 1e-6 + atol 1.2e-7 otherwise
+    for op in ["neg", "exp", "log", "sqrt", "relu", "sigmoid", "tanh"]:
+        text = f"input x : f32{shape}\ny = {op} x\noutput y"
+        positive = op in ("log", "sqrt")
+        g, ins = oracle_inputs(oracle, text, seed=11, lo=0.01 if positive else -6.0, hi=6.0)
+        got = run_graph(mc, text=text, passes="none", inputs=ins)[0]
+        if op in ("neg", "relu", "sqrt"):
+            want = oracle.evaluate_f32(g, ins)[0]
+            assert np.array_equal(got, want), op  # IEEE-exact on both sides (sqrtf is correctly rounded)
+        else:
+            ok, msg = all_close(got, oracle.evaluate_f64(g, ins)[0], 1e-6, 1.2e-7)
+            assert ok, f"{op} {shape}: {msg}"
+
+
+BROADCASTS = [("[17, 33]", "[17, 33]"), ("[17, 32]", "[]"), ("[]", "[17, 33]"), ("[17, 32]", "[32]"), ("[17, 33]", "[17, 1]"),
+              ("[17, 1]", "[1, 33]"), ("[2, 3, 4]", "[3, 1]"), ("[5, 1, 6]", "[1, 4, 1]"), ("[16, 64]", "[16, 1]"),
+              ("[4, 8, 16]", "[8, 1]"), ("[4, 8, 16]", "[4, 1, 16]")]
+
+
+@pytest.mark.parametrize("sa,sb", BROADCASTS)
+def test_binary_ops_are_bit_exact_for_every_broadcast_pattern(mc, oracle, sa, sb):
+    # tests/test_cuda_backend.cpp:103-117
+    for op in ["add", "sub", "mul", "div"]:
+        text = f"input a : f32{sa}\ninput b : f32{sb}\ny = {op} a, b\noutput y"
+        g, ins = oracle_inputs(oracle, text, seed=5, lo=0.5, hi=2.0)
+        for options in ({}, {"vectorize": 0}, {"unroll": 1}):
+            got = run_graph(mc, text=text, passes="none", options=options, inputs=ins)[0]
+            assert np.array_equal(got, oracle.evaluate_f32(g, ins)[0]), (op, sa, sb, options)
+
+
+def test_fused_arithmetic_is_bit_exact_and_tails_are_covered(mc, oracle):
+    # A fused group of IEEE-exact ops must equal the oracle bit for bit (no FMA contraction), at sizes that
+    # end inside a trip, inside a vector and inside a block.
+    for n in [1, 3, 4, 1023, 1024, 1025, 4096 + 4, 256 * 4 * 4 * 3 + 8]:
+        text = (f"input x : f32[{n}]\ninput y : f32[{n}]\nconst c : f32[] = 0.3\n"
+                "a = mul x, y\nb = add a, x\nd = mul b, c\ne = sub d, y\nf = div e, b\noutput f")
+        g, ins = oracle_inputs(oracle, text, seed=2, lo=0.5, hi=2.0)
+        got = run_graph(mc, text=text, inputs=ins)[0]
+        assert np.array_equal(got, oracle.evaluate_f32(g, ins)[0]), n
+
+
+def test_benchmark_graphs_fused_and_unfused_match_the_oracle(mc, oracle):
+    # tests/test_cuda_backend.cpp:395-416: rtol 1e-5, atol 1e-5 * max|expected|
+    cases = [("ref_gelu_chain", "M=64,N=256", 1e-5), ("ref_matmul_bias_relu", "M=64,K=256,N=128", 1e-4),
+             ("ref_mlp_block", "B=32,D=128,H=256", 1e-4)]
+    for name, dims, rtol in cases:
+        path = str(GOLDEN / "graphs" / f"{name}.mcg")
+        g, ins = oracle_inputs(oracle, path=path, dims=dims)
+        want = oracle.evaluate_f64(g, ins)[0]
+        scale = float(np.max(np.abs(want)))
+        for passes in ["none", "default"]:
+            for options in ({}, {"fuse_epilogue": 0}):
+                got = run_graph(mc, path=path, dims=dims, passes=passes, options=options, inputs=ins)[0]
+                ok, msg = all_close(got, want, rtol, rtol * scale)
+                assert ok, f"{name} {passes} {options}: {msg}"
+
+
+def test_random_graphs_match_the_reference_evaluator(mc, oracle):
+    # tests/test_cuda_backend.cpp:418-437: 1e-4 * scale, optimized and unoptimized; the expected values are the
+    # reference's own evaluator outputs (tests/golden/evaluator.npz).
+    gold = json.loads((GOLDEN / "host_logic.json").read_text())["random"]
+    expected = np.load(GOLDEN / "evaluator.npz")
+    for seed, entry in gold.items():
+        g = oracle.parse_mcg(entry["mcg"])
+        ins = oracle.make_random_inputs(g, 1)
+        for passes in ["none", "default"]:
+            outs = run_graph(mc, text=entry["mcg"], passes=passes, inputs=ins)
+            for k, got in enumerate(outs):
+                want = expected[f"random/{seed}/out{k}"]
+                scale = max(1.0, float(np.max(np.abs(want))))
+                ok, msg = all_close(got, want, 1e-4, 1e-4 * scale)
+                assert ok, f"random graph {seed}, passes {passes}, output {k}: {msg}"
+
+
+def test_buffer_reuse_launch_counts_and_repeatability(mc, oracle):
+    # tests/test_cuda_backend.cpp:439-482
+    chain = "input x : f32[1024]\n" + "".join(f"t{i} = tanh {'x' if i == 0 else 't' + str(i - 1)}\n" for i in range(8)) + "output t7"
+    with mc.CompiledGraph(text=chain, passes="none") as exe:
+        assert exe.intermediate_bytes == 2 * 4096 and exe.kernel_launches == 8
+    path = str(GOLDEN / "graphs" / "ref_gelu_chain.mcg")
+    for passes, launches in [("none", 11), ("dne,fold,dne", 9), ("default", 1)]:
+        with mc.CompiledGraph(path, dims="M=16,N=64", passes=passes) as exe:
+            assert exe.kernel_launches == launches
+    path = str(GOLDEN / "graphs" / "ref_mlp_block.mcg")
+    g, ins = oracle_inputs(oracle, path=path, dims="B=64,D=128,H=256")
+    with mc.CompiledGraph(path, dims="B=64,D=128,H=256") as exe:
+        first = exe.run(ins)[0].copy()
+        exe.upload(ins)
+        exe.enqueue()
+        exe.enqueue()
+        again = exe.download()[0]
+        assert np.array_equal(first, again)
+        with pytest.raises(mc.McError, match="expected 1 inputs, got 2"):
+            exe.run([ins[0], ins[0]])
+
+
+def test_outputs_that_are_inputs_or_constants(mc, oracle):
+    text = "input x : f32[8]\nconst c : f32[4] = [1, 2, 3, 4]\ny = exp x\noutput x, c, y"
+    g, ins = oracle_inputs(oracle, text)
+    outs = run_graph(mc, text=text, inputs=ins)
+    assert np.array_equal(outs[0], ins[0]) and list(outs[1]) == [1, 2, 3, 4]
+
+
+# ------------------------------------------------------------------ matmuls
+
+FP32_SHAPES = [(1, 1, 1), (3, 5, 7), (1, 1000, 1), (33, 257, 65), (65, 9, 63), (127, 129, 131), (128, 128, 128),
+               (129, 13, 129), (256, 256, 256), (16, 4099, 16), (513, 77, 259), (129, 132, 260), (300, 1004, 36), (2, 12, 4)]
+TC_SHAPES = [(1, 1, 1), (3, 5, 7), (33, 257, 65), (127, 129, 131), (128, 128, 128), (129, 33, 129), (16, 4099, 16),
+             (300, 1004, 36), (2, 12, 4), (256, 256, 256), (384, 512, 640)]
+
+
+def matmul_text(m, k, n):
+    return f"input a : f32[{m}, {k}]\ninput w : f32[{k}, {n}]\nc = matmul a, w\noutput c"
+
+
+def exact_and_abs(a, b):
+    a64, b64 = a.astype(np.float64), b.astype(np.float64)
+    return a64 @ b64, np.abs(a64) @ np.abs(b64)
+
+
+def check_bound(got, exact, abs_dot, k, u_in, subnormals, label):
+    gamma = k * U32 / (1.0 - k * U32)
+    if u_in == 0.0:
+        bound = 2.0 * gamma * abs_dot + 2.0 * U32 * np.abs(exact)
+    else:
+        tiny = 2.0 * k * 2.0 ** -25 if subnormals else 0.0
+        bound = (2.0 * u_in + u_in * u_in + 2.0 * gamma) * abs_dot + 2.0 * U32 * np.abs(exact) + tiny
+    err = np.abs(got.astype(np.float64).reshape(exact.shape) - exact)
+    bad = ~(err <= bound)
+    assert not bad.any(), (f"{label}: {int(bad.sum())} of {bad.size} outside the bound; first at {np.argwhere(bad)[0].tolist()} "
+                           f"got {got.reshape(exact.shape)[tuple(np.argwhere(bad)[0])]!r} exact {exact[tuple(np.argwhere(bad)[0])]!r}")
+
+
+@pytest.mark.parametrize("kernel", ["auto", "split_k", "double_buffered", "naive"])
+def test_fp32_matmul_within_the_dot_product_bound(mc, oracle, kernel):
+    # tests/test_cuda_backend.cpp:119-162
+    for m, k, n in FP32_SHAPES:
+        text = matmul_text(m, k, n)
+        g, ins = oracle_inputs(oracle, text, seed=3)
+        got = run_graph(mc, text=text, options={"matmul": kernel}, inputs=ins)[0]
+        exact, abs_dot = exact_and_abs(ins[0], ins[1])
+        check_bound(got, exact, abs_dot, k, 0.0, False, f"{kernel} {m}x{k}x{n}")
+
+
+def _torch():
+    import torch
+
+    return torch
+
+
+def _device_gemm(mc, arith, a, b, splits, b_transposed=False, half=None):
+    """Calls mcd_gemm directly with device buffers held by torch; C is pre-filled with NaN."""
+    torch = _torch()
+    lib = mc.lib()
+
+    class GemmArgs(C.Structure):
+        _fields_ = [("arith", C.c_int), ("m", C.c_int), ("n", C.c_int), ("k", C.c_int), ("a", C.c_void_p), ("b", C.c_void_p),
+                    ("lda", C.c_longlong), ("ldb", C.c_longlong), ("b_transposed", C.c_int), ("c", C.c_void_p),
+                    ("ldc", C.c_longlong), ("c16", C.c_void_p), ("c16_kind", C.c_int), ("ldc16", C.c_longlong),
+                    ("splits", C.c_int), ("workspace", C.c_void_p), ("function", C.c_void_p), ("reduce_function", C.c_void_p),
+                    ("epilogue_inputs", C.c_void_p * 6), ("num_epilogue_inputs", C.c_int), ("status", C.c_void_p),
+                    ("variant", C.c_int)]
+
+    m, k = a.shape
+    n = b.shape[1]
+    dev = torch.device("cuda:0")
+    ta = torch.from_numpy(a).to(dev)
+    tb = torch.from_numpy(b).to(dev)
+    if half is not None:
+        dt = torch.bfloat16 if half == "bf16" else torch.float16
+        kp, np_ = (k + 7) // 8 * 8, (n + 7) // 8 * 8
+        pa = torch.zeros((m, kp), dtype=dt, device=dev)
+        pa[:, :k] = ta.to(dt)
+        if b_transposed:
+            pb = torch.zeros((n, kp), dtype=dt, device=dev)
+            pb[:, :k] = tb.t().to(dt)
+            ldb = kp
+        else:
+            pb = torch.zeros((k, np_), dtype=dt, device=dev)
+            pb[:, :n] = tb.to(dt)
+            ldb = np_
+        ta, tb, lda = pa, pb, kp
+    else:
+        lda = k
+        if b_transposed:
+            tb = tb.t().contiguous()
+            ldb = k
+        else:
+            ldb = n
+    tc = torch.full((m, n), float("nan"), dtype=torch.float32, device=dev)
+    ws = torch.full((max(1, splits) * m * n,), float("nan"), dtype=torch.float32, device=dev)
+    status = torch.zeros(64, dtype=torch.int32, device=dev)
+    args = GemmArgs()
+    args.arith, args.m, args.n, args.k = arith, m, n, k
+    args.a, args.b, args.lda, args.ldb, args.b_transposed = ta.data_ptr(), tb.data_ptr(), lda, ldb, int(b_transposed)
+    args.c, args.ldc, args.splits, args.workspace = tc.data_ptr(), n, splits, ws.data_ptr()
+    args.status = status.data_ptr()
+    lib.mcd_gemm.restype = C.c_int
+    lib.mcd_last_error.restype = C.c_char_p
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = lib.mcd_gemm(C.byref(args), C.c_void_p(stream))
+    assert rc == 0, lib.mcd_last_error().decode()
+    torch.cuda.synchronize()
+    assert int(status[0].item()) == 0, f"kernel gave up a wait: status {int(status[0].item()):#x}"
+    return tc.cpu().numpy()
+
+
+def test_forced_split_counts_fp32(mc, oracle):
+    # tests/test_cuda_backend.cpp:241-313: any split count, C pre-filled with NaN
+    for m, k, n in [(33, 1000, 65), (128, 2048, 512), (16, 4099, 16), (2, 12, 4), (129, 260, 132), (64, 5, 8)]:
+        a = oracle.uniform_values(m * k, 1, -1, 1).reshape(m, k)
+        b = oracle.uniform_values(k * n, 2, -1, 1).reshape(k, n)
+        exact, abs_dot = exact_and_abs(a, b)
+        for splits in [1, 2, 3, 7, 16, 64]:
+            got = _device_gemm(mc, 0, a, b, splits)
+            check_bound(got, exact, abs_dot, k, 0.0, False, f"fp32 {m}x{k}x{n} splits={splits}")
+
+
+TC_KINDS = [("tensor_core_bf16", 2, "bf16", 2.0 ** -8, False), ("tensor_core_f16", 3, "f16", 2.0 ** -11, True),
+            ("tensor_core_tf32", 1, None, 2.0 ** -11, False)]
+
+
+@pytest.mark.parametrize("layout", [False, True])
+@pytest.mark.parametrize("name,arith,half,u,sub", TC_KINDS)
+def test_tensor_core_kernel_direct(mc, oracle, name, arith, half, u, sub, layout):
+    """The tcgen05 kernels through the device layer, both layouts of B, with and without a K split."""
+    if half is None and not layout:
+        pytest.skip("TF32 reads B as a [n,k] copy only")
+    for m, k, n in [(128, 64, 256), (128, 256, 256), (256, 512, 512), (300, 1004, 36), (33, 264, 72), (1024, 1024, 1024)]:
+        if half is None and (k % 4 or n % 4):
+            continue
+        a = oracle.uniform_values(m * k, 1, -1, 1).reshape(m, k)
+        b = oracle.uniform_values(k * n, 2, -1, 1).reshape(k, n)
+        exact, abs_dot = exact_and_abs(a, b)
+        for splits in [1, 3]:
+            got = _device_gemm(mc, arith, a, b, splits, b_transposed=layout, half=half)
+            check_bound(got, exact, abs_dot, k, u, sub, f"{name} {m}x{k}x{n} splits={splits} transposed={layout}")
+
+
+@pytest.mark.parametrize("name,arith,half,u,sub", TC_KINDS)
+def test_tensor_core_matmuls_within_their_precision_bounds(mc, oracle, name, arith, half, u, sub):
+    # tests/test_cuda_backend.cpp:164-219
+    for m, k, n in TC_SHAPES:
+        text = matmul_text(m, k, n)
+        g, ins = oracle_inputs(oracle, text, seed=3)
+        exact, abs_dot = exact_and_abs(ins[0], ins[1])
+        for layout in ["kn", "transposed"]:
+            with mc.CompiledGraph(text=text, options={"matmul": name, "b_layout": layout}) as exe:
+                got = exe.run(ins)[0]
+                kernels = exe.matmul_kernels
+            check_bound(got, exact, abs_dot, k, u, sub, f"{name} {m}x{k}x{n} {layout} ran {kernels}")
+
+
+# -------------------------------------------------- the benchmark configs, small
+
+
+def norm_scaled_error(got, want):
+    want = want.astype(np.float64)
+    return float(np.max(np.abs(got.astype(np.float64) - want)) / max(1e-30, np.sqrt(np.mean(want ** 2))))
+
+
+def test_config_graphs_small(mc, oracle):
+    cases = [("c1_mlp_block", "B=64", "uniform"), ("c3_ffn", "T=256,D=128,H=512", "normal"),
+             ("c5_mlp_stack", "B=256,D=256", "normal")]
+    for name, dims, dist in cases:
+        path = mc.graph_path(name)
+        d = {k: int(v) for k, v in (kv.split("=") for kv in dims.split(","))}
+        g = oracle.parse_mcg_file(path, d)
+        shape = g.node(g.inputs[0]).shape
+        n = int(np.prod(shape))
+        x = oracle.uniform_values(n, 1, -1, 1) if dist == "uniform" else oracle.normal_values(n, 1)
+        ins = [x.reshape(shape)]
+        want = oracle.evaluate_f64(g, ins)[0]
+        scale = float(np.max(np.abs(want)))
+        for matmul, tol in [("auto", 1e-4), ("tensor_core_tf32", 5e-3), ("tensor_core_bf16", 2e-2), ("tensor_core_f16", 2e-2)]:
+            for fuse in (1, 0):
+                got = run_graph(mc, path=path, dims=dims, options={"matmul": matmul, "fuse_epilogue": fuse}, inputs=ins)[0]
+                if matmul == "auto":
+                    ok, msg = all_close(got, want, tol, tol * scale)
+                    assert ok, f"{name} {matmul} fuse={fuse}: {msg}"
+                else:
+                    err = norm_scaled_error(got, want)
+                    # deep stacks accumulate the per-layer rounding; the bar is per matmul layer
+                    layers = 8 if name.startswith("c5") else 2 if name.startswith("c3") else 1
+                    assert err <= tol * layers, f"{name} {matmul} fuse={fuse}: norm-scaled error {err:.3e}"
+
+
+def test_c2_gelu_full_size_properties(mc, oracle):
+    """At the full 8192 x 8192 size: gelu(x) - gelu(-x) == x (odd-part identity), and sampled rows equal the oracle."""
+    path = mc.graph_path("c2_gelu_chain")
+    n = 8192 * 8192
+    x = oracle.normal_values(n, 7)
+    with mc.CompiledGraph(path) as exe:
+        y_pos = exe.run([x])[0]
+        y_neg = exe.run([-x])[0]
+    resid = np.abs((y_pos.astype(np.float64) - y_neg.astype(np.float64)) - x)
+    assert float(resid.max()) <= 1e-5 * max(1.0, float(np.abs(x).max()))
+    rows = [0, 1, 4095, 8191]
+    g = oracle.parse_mcg_file(path, {"M": len(rows), "N": 8192})
+    sample = np.stack([x.reshape(8192, 8192)[r] for r in rows])
+    want = oracle.evaluate_f64(g, [sample])[0]
+    got = np.stack([y_pos.reshape(8192, 8192)[r] for r in rows]).reshape(-1)
+    ok, msg = all_close(got, want, 1e-5, 1e-7)
+    assert ok, msg
+
+
+def test_large_matmul_sampled_and_checksum(mc, oracle):
+    """4096^3 in every arithmetic: 1000 sampled dot products in float64 (bench/bench_cuda.cpp:386-436) and the
+    row-sum identity C 1 = A (B 1)."""
+    m = k = n = 4096
+    a = oracle.uniform_values(m * k, 1, -1, 1).reshape(m, k)
+    b = oracle.uniform_values(k * n, 2, -1, 1).reshape(k, n)
+    rng = np.random.default_rng(0)
+    rows, cols = rng.integers(0, m, 1000), rng.integers(0, n, 1000)
+    exact, abs_dot = oracle.sampled_matmul_f64(a, b, rows, cols)
+    rowsum = a.astype(np.float64) @ b.astype(np.float64).sum(axis=1)
+    text = matmul_text(m, k, n)
+    for name, u, sub in [("auto", 0.0, False), ("tensor_core_tf32", 2.0 ** -11, False), ("tensor_core_bf16", 2.0 ** -8, False),
+                         ("tensor_core_f16", 2.0 ** -11, True)]:
+        got = run_graph(mc, text=text, options={"matmul": name}, inputs=[a, b])[0].reshape(m, n)
+        check_bound(got[rows, cols], exact, abs_dot, k, u, sub, f"{name} 4096^3 sampled")
+        scale = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64).sum(axis=1)
+        rel = np.max(np.abs(got.astype(np.float64).sum(axis=1) - rowsum) / scale)
+        assert rel <= (2 * u + 4096 * U32 * 2), f"{name}: row-sum identity off by {rel:.3e}"
