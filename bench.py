@@ -131,27 +131,36 @@ def make_inputs(oracle, graph, dist, seed):
     return ins
 
 
-def cpu_sample_rate(oracle, path, dims, batch_dim, kind, dist, seconds_target=10.0):
-    """Times the CPU oracle (float32, reference CPU-backend semantics) on a row sample of the workload."""
+def cpu_sample(oracle, path, dims, batch_dim, kind, dist, rows_cap):
+    """The CPU port (oracle/cpu_baseline.py over oracle_kernels.c) prepared on a row sample of the workload."""
+    from oracle import cpu_baseline
+
     sample_dims = dict(dims)
     lead = batch_dim or ("M" if "M" in dims else None)
     rows_full = dims[lead] if lead else 1
-    rows = min(rows_full, 512 if kind == "bytes" else 256)
+    rows = min(rows_full, rows_cap)
     if lead:
         sample_dims[lead] = rows
     g = oracle.parse_mcg_file(path, sample_dims)
+    threads = cpu_baseline.max_threads()
+    plan = cpu_baseline.CpuPlan(g, threads)
     ins = make_inputs(oracle, g, dist, 1)
-    oracle.evaluate_f32(g, ins)  # warm
+    return plan, ins, algorithmic_work(oracle, g, kind), threads, f"{rows} of {rows_full} rows of '{lead}'"
+
+
+def cpu_sample_rate(oracle, path, dims, batch_dim, kind, dist, seconds_target=10.0):
+    """Times the CPU port on a bounded sample; returns (rate, threads, description)."""
+    plan, ins, work, threads, what = cpu_sample(oracle, path, dims, batch_dim, kind, dist, 2048 if kind == "bytes" else 1024)
+    plan.run(ins)  # warm
     t0, reps = time.perf_counter(), 0
     while True:
-        oracle.evaluate_f32(g, ins)
+        plan.run(ins)
         reps += 1
         dt = time.perf_counter() - t0
-        if dt > seconds_target or reps >= 50:
+        if dt > seconds_target or reps >= 200:
             break
-    work = algorithmic_work(oracle, g, kind)
     rate = work * reps / dt / (1e9 if kind == "bytes" else 1e12)
-    return rate, f"{rows} of {rows_full} rows of '{lead}', {reps} runs in {dt:.1f} s, numpy float32 (elementwise 1 thread; matmul BLAS)"
+    return rate, threads, f"{what}, {reps} runs in {dt:.1f} s, C port of the reference CPU kernels with {threads} OpenMP threads"
 
 
 def run_reference_arm(args):
@@ -163,32 +172,23 @@ def run_reference_arm(args):
 
     name, dims, matmul, batch_dim, kind, dist = WORKLOADS[args.workload]
     path = mc.graph_path(name)
-    sample_dims = dict(dims)
-    lead = batch_dim or ("M" if "M" in dims else None)
-    rows = min(dims[lead], 256 if kind == "bytes" else 128) if lead else 1
-    if lead:
-        sample_dims[lead] = rows
-    g = oracle.parse_mcg_file(path, sample_dims)
-    ins = make_inputs(oracle, g, dist, 1)
-    work = algorithmic_work(oracle, g, kind)
+    plan, ins, work, threads, what = cpu_sample(oracle, path, dims, batch_dim, kind, dist, 2048 if kind == "bytes" else 1024)
     for _ in range(max(1, min(args.warmup, 3))):
-        oracle.evaluate_f32(g, ins)
+        plan.run(ins)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        oracle.evaluate_f32(g, ins)
+        plan.run(ins)
     dt = time.perf_counter() - t0
     unit = "GB/s" if kind == "bytes" else "TFLOP/s"
     value = work * args.steps / dt / (1e9 if kind == "bytes" else 1e12)
-    cores = os.cpu_count() or 1
     line = {
         "impl": "reference", "metric": "fused-eltwise HBM GB/s" if kind == "bytes" else "graph TFLOP/s", "value": value, "unit": unit,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "graph": name, "dims": dims,
-                   "note": "reference CPU path = oracle port (Eigen 3.4.0 is absent, the reference's CPU backend cannot be built); "
-                           f"each step runs a {rows}-row sample of the workload"},
-        "cpu_baseline": {"value": value, "unit": unit, "cores": cores if kind != "bytes" else 1, "kind": "port",
-                         "sample": f"{rows} rows per step, numpy float32"},
+                   "note": "reference CPU path = C port of its CPU kernels (Eigen 3.4.0 is absent, so the reference's own CPU "
+                           f"backend cannot be built); each step runs {what}"},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "port", "sample": f"{what} per step"},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -339,9 +339,8 @@ def main():
 
         cpu = None
         if with_cpu and rank == 0:
-            rate, sample = cpu_sample_rate(oracle, path, dims, batch_dim, kind, dist_name)
-            cpu = {"value": rate, "unit": "GB/s" if kind == "bytes" else "TFLOP/s", "cores": 1 if kind == "bytes" else (os.cpu_count() or 1),
-                   "kind": "port", "sample": sample}
+            rate, threads, sample = cpu_sample_rate(oracle, path, dims, batch_dim, kind, dist_name)
+            cpu = {"value": rate, "unit": "GB/s" if kind == "bytes" else "TFLOP/s", "cores": threads, "kind": "port", "sample": sample}
 
         result = {
             "metric": "fused-eltwise HBM GB/s" if kind == "bytes" else "graph TFLOP/s", "value": value,
