@@ -348,7 +348,7 @@ private:
         auto launch = std::make_unique<Launch>();
         launch->kind = Launch::Kind::Elementwise;
         double ms = 0.0;
-        if (mcd_jit_kernel(options_.device, kernel.source.c_str(), kElementwiseKernelName, "--fmad=false", &launch->function,
+        if (mcd_jit_kernel(options_.device, kernel.source.c_str(), kElementwiseKernelName, options_.eltwise_fmad ? "--fmad=true" : "--fmad=false", &launch->function,
                            &ms) != 0) {
             return Error{std::string("compiling the kernel of '") + node.name + "' failed: " + mcd_last_error()};
         }
@@ -359,6 +359,7 @@ private:
         launch->count = static_cast<unsigned>(kernel.vectorized ? n / 4 : n);
         int blocks_per_sm = 0;
         MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(kElementwiseBlock), 0, &blocks_per_sm));
+        if (options_.eltwise_blocks_per_sm > 0) blocks_per_sm = std::min(blocks_per_sm, options_.eltwise_blocks_per_sm);
         // One wave of resident blocks at most; the tile loop inside the kernel covers the rest.
         const std::size_t per_block = static_cast<std::size_t>(kElementwiseBlock) * kernel.unroll;
         const std::size_t wanted = (launch->count + per_block - 1) / per_block;

@@ -68,6 +68,11 @@ struct CudaOptions {
     unsigned eltwise_unroll = 4;
     bool streaming_hints = true;
     int gemm_variant = 0;
+    bool eltwise_fmad = false;      // let the compiler contract a*b+c in generated kernels (not bit-exact vs the CPU)
+    // Cap on resident blocks per SM for the one-wave grid (0 = whatever occupancy allows). On B200 four
+    // 256-thread blocks with four 128-bit loads in flight per thread stream faster than eight (6.1 vs
+    // 5.5 TB/s on the 512 MiB GELU pass): more outstanding requests than that only queue up in front of HBM.
+    int eltwise_blocks_per_sm = 4;
 };
 
 enum class Arith : int { F32 = 0, Tf32 = 1, Bf16 = 2, F16 = 3 };  // same numbering as MCD_GEMM_*
