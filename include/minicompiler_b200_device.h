@@ -162,6 +162,30 @@ MCD_API size_t mcd_gemm_dynamic_smem(int arith);
 /* Whether tcgen05 kernels can run on `device` (compute capability 10.x). */
 MCD_API int mcd_tensor_core_supported(int device, int arith);
 
+/* Bytes of built-in scratch behind mcd_gemm_f32_split_no_alloc (held by every GPU that loads
+ * the library, until the process exits). */
+#define MCD_NO_ALLOC_SCRATCH_BYTES (16u << 20)
+
+/* FP32 split-K matmul that allocates nothing: C[m,n] = A[m,k] * B[k,n], all dense row-major
+ * float (lda = k, ldb = n, ldc = n), K divided into `splits` slices whose partial sums are
+ * added in slice order, exactly as mcd_gemm(MCD_GEMM_F32) does with a caller workspace - and
+ * bit-identical to it for the same split count.
+ *
+ * It has no counterpart in the reference. It exists for callers that cannot call cudaMalloc:
+ * a process whose own pool already owns all of HBM, or code on a latency-critical path that
+ * cannot take the device-wide synchronisation an allocation implies. The partial sums go to
+ * an array built into the library instead of a workspace, so
+ *   - slices * m * n * 4 bytes must not exceed MCD_NO_ALLOC_SCRATCH_BYTES (the call fails with
+ *     a message otherwise; use fewer splits or mcd_gemm with your own workspace);
+ *   - all calls on one GPU share that array: two calls that overlap on the GPU (different
+ *     streams) race on it. Calls on one stream are safe. Nothing in it needs clearing between
+ *     calls, every partial sum is rewritten before it is read;
+ *   - the first call on each GPU looks up the array's device address (cudaGetSymbolAddress) with
+ *     that GPU current; make that first call before starting any stream capture.
+ * It calls no cudaMalloc, cudaFree or allocating library routine. */
+MCD_API int mcd_gemm_f32_split_no_alloc(const float* a, const float* b, float* c, int m, int n, int k, int splits,
+                                        void* stream);
+
 #ifdef __cplusplus
 }
 #endif
