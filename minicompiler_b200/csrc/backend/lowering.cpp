@@ -338,14 +338,20 @@ std::string generate_epilogue_source(const Graph& graph, const Step& step) {
        << graph.node(step.result).name << "' (" << step.program.num_ops() << " elementwise op(s)).\n";
     os << "#define MC_EPILOGUE_DEFINED 1\n";
     os << "struct McEpilogueArgs {\n    const float* p[6];\n};\n";
-    os << "__device__ __forceinline__ float mc_epilogue(float acc, unsigned row, unsigned col, const McEpilogueArgs& e) {\n";
-    os << "    (void)row;\n    (void)col;\n    (void)e;\n";
     // Program input k -> slot in McEpilogueArgs::p (accumulator loads take none).
     std::vector<int> slot(step.inputs.size(), -1);
-    int next = 0;
+    std::vector<std::size_t> input_of_slot;
     for (std::size_t k = 0; k < step.inputs.size(); ++k) {
-        if (!step.load_is_accumulator[k]) slot[k] = next++;
+        if (step.load_is_accumulator[k]) continue;
+        slot[k] = static_cast<int>(input_of_slot.size());
+        input_of_slot.push_back(k);
     }
+    const std::size_t slots = input_of_slot.size();
+
+    // The straight-line program on values: the accumulator and one value per extra operand.
+    os << "__device__ __forceinline__ float mc_epi_eval(float acc";
+    for (std::size_t s = 0; s < slots; ++s) os << ", float x" << s;
+    os << ") {\n    (void)acc;\n";
     for (std::size_t r = 0; r < step.program.instrs.size(); ++r) {
         const FusedInstr& ins = step.program.instrs[r];
         os << "    const float r" << r << " = ";
@@ -354,16 +360,8 @@ std::string generate_epilogue_source(const Graph& graph, const Step& step) {
                 const auto k = static_cast<std::size_t>(ins.a);
                 if (step.load_is_accumulator[k]) {
                     os << "acc";
-                    break;
-                }
-                const std::string p = "e.p[" + std::to_string(slot[k]) + "]";
-                switch (step.operands[k].kind) {
-                    case EpilogueOperand::Kind::Scalar: os << "__ldg(" << p << ")"; break;
-                    case EpilogueOperand::Kind::Row: os << "__ldg(" << p << " + col)"; break;
-                    case EpilogueOperand::Kind::Column: os << "__ldg(" << p << " + row)"; break;
-                    case EpilogueOperand::Kind::Full:
-                        os << "__ldg(" << p << " + ((unsigned long long)row * " << step.n << "ull + col))";
-                        break;
+                } else {
+                    os << "x" << slot[k];
                 }
                 break;
             }
@@ -381,6 +379,62 @@ std::string generate_epilogue_source(const Graph& graph, const Step& step) {
         os << ";\n";
     }
     os << "    return r" << step.program.instrs.size() - 1 << ";\n}\n";
+
+    auto kind_of = [&](std::size_t s) { return step.operands[input_of_slot[s]].kind; };
+    auto scalar_address = [&](std::size_t s, const std::string& row, const std::string& col) {
+        const std::string p = "e.p[" + std::to_string(s) + "]";
+        switch (kind_of(s)) {
+            case EpilogueOperand::Kind::Scalar: return p;
+            case EpilogueOperand::Kind::Row: return p + " + " + col;
+            case EpilogueOperand::Kind::Column: return p + " + " + row;
+            case EpilogueOperand::Kind::Full: return p + " + ((unsigned long long)" + row + " * " + std::to_string(step.n) + "ull + " + col + ")";
+        }
+        return p;
+    };
+
+    // One element.
+    os << "__device__ __forceinline__ float mc_epilogue(float acc, unsigned row, unsigned col, const McEpilogueArgs& e) {\n";
+    os << "    (void)row;\n    (void)col;\n    (void)e;\n";
+    os << "    return mc_epi_eval(acc";
+    for (std::size_t s = 0; s < slots; ++s) os << ", __ldg(" << scalar_address(s, "row", "col") << ")";
+    os << ");\n}\n";
+
+    // 32 consecutive columns of one row, all in range, col0 a multiple of 32: row and full operands come
+    // in as 128-bit loads (the operand bases are 256-byte aligned; a full operand needs n % 4 == 0).
+    const bool wide_full = step.n % 4 == 0;
+    os << "#define MC_EPILOGUE32_DEFINED 1\n";
+    os << "__device__ __forceinline__ void mc_epilogue32(float (&f)[32], unsigned row, unsigned col0, const McEpilogueArgs& e) {\n";
+    os << "    (void)row;\n    (void)col0;\n    (void)e;\n";
+    for (std::size_t s = 0; s < slots; ++s) {
+        if (kind_of(s) == EpilogueOperand::Kind::Scalar || kind_of(s) == EpilogueOperand::Kind::Column) {
+            os << "    const float s" << s << " = __ldg(" << scalar_address(s, "row", "col0") << ");\n";
+        }
+    }
+    os << "#pragma unroll\n    for (int q = 0; q < 8; ++q) {\n";
+    for (std::size_t s = 0; s < slots; ++s) {
+        const bool wide = kind_of(s) == EpilogueOperand::Kind::Row || (kind_of(s) == EpilogueOperand::Kind::Full && wide_full);
+        if (wide) {
+            os << "        const float4 v" << s << " = __ldg(reinterpret_cast<const float4*>(" << scalar_address(s, "row", "col0")
+               << ") + q);\n";
+        } else if (kind_of(s) == EpilogueOperand::Kind::Full) {
+            os << "        const float* u" << s << " = " << scalar_address(s, "row", "col0") << " + 4 * q;\n";
+            os << "        const float4 v" << s << " = make_float4(__ldg(u" << s << "), __ldg(u" << s << " + 1), __ldg(u" << s
+               << " + 2), __ldg(u" << s << " + 3));\n";
+        }
+    }
+    for (const char* lane : {"x", "y", "z", "w"}) {
+        const int j = lane[0] == 'x' ? 0 : lane[0] == 'y' ? 1 : lane[0] == 'z' ? 2 : 3;
+        os << "        f[4 * q + " << j << "] = mc_epi_eval(f[4 * q + " << j << "]";
+        for (std::size_t s = 0; s < slots; ++s) {
+            if (kind_of(s) == EpilogueOperand::Kind::Scalar || kind_of(s) == EpilogueOperand::Kind::Column) {
+                os << ", s" << s;
+            } else {
+                os << ", v" << s << "." << lane;
+            }
+        }
+        os << ");\n";
+    }
+    os << "    }\n}\n";
     return os.str();
 }
 

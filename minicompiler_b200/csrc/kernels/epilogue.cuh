@@ -18,6 +18,16 @@ __device__ __forceinline__ float mc_epilogue(float acc, unsigned row, unsigned c
 }
 #endif
 
+#ifndef MC_EPILOGUE32_DEFINED
+#define MC_EPILOGUE32_DEFINED 0
+// The epilogue over 32 consecutive in-range columns of one row (col0 a multiple of 32); a generated
+// one fetches row and full-shape operands with 128-bit loads instead of one load per element.
+__device__ __forceinline__ void mc_epilogue32(float (&f)[32], unsigned row, unsigned col0, const McEpilogueArgs& e) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = mc_epilogue(f[j], row, col0 + j, e);
+}
+#endif
+
 #ifndef MC_HALF_HELPERS
 #define MC_HALF_HELPERS
 // Round-to-nearest-even conversions to the 16-bit operand formats (kind 1 = bf16, 2 = fp16).

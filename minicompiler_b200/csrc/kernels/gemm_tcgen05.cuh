@@ -12,8 +12,8 @@
 //   * warp 1 (one lane) issues tcgen05.mma (128 x 256 x 16 for 16-bit operands,
 //     128 x 256 x 8 for TF32) from shared-memory descriptors into a TMEM
 //     accumulator and releases each stage with tcgen05.commit;
-//   * warps 2-5 drain the accumulator with tcgen05.ld (each warp owns 32 TMEM
-//     lanes = 32 rows), apply the fused epilogue and store C as FP32 and/or as a
+//   * warps 2-9 drain the accumulator with tcgen05.ld (each warp owns 32 TMEM
+//     lanes = 32 rows and one half of the columns), apply the fused epilogue and store C as FP32 and/or as a
 //     16-bit copy for a downstream tensor-core matmul. TMEM holds two 256-column
 //     accumulators, so the epilogue of one tile overlaps the main loop of the next.
 //
@@ -28,7 +28,8 @@
 #define MC_TC_BM 128
 #define MC_TC_BN 256
 #define MC_TC_STAGES 4
-#define MC_TC_THREADS 192
+#define MC_TC_EPILOGUE_WARPS 8
+#define MC_TC_THREADS (64 + 32 * MC_TC_EPILOGUE_WARPS)
 #define MC_TC_A_BYTES (MC_TC_BM * 128)
 #define MC_TC_B_BYTES (MC_TC_BN * 128)
 #define MC_TC_STAGE_BYTES (MC_TC_A_BYTES + MC_TC_B_BYTES)
@@ -221,7 +222,7 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
         }
         for (int a = 0; a < 2; ++a) {
             mc_mbar_init(bar_tmem_full + 8 * a, 1);
-            mc_mbar_init(bar_tmem_empty + 8 * a, 4);  // one arrival per epilogue warp
+            mc_mbar_init(bar_tmem_empty + 8 * a, MC_TC_EPILOGUE_WARPS);  // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -344,6 +345,9 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
     } else {
         // ---------------------------------------------------------------- epilogue
         const int quarter = warp & 3;  // the TMEM lanes this warp may touch: [32*quarter, +32)
+        // Two warps share each lane quarter and take one half of the tile's columns each.
+        constexpr int kColsPerWarp = MC_TC_BN / (MC_TC_EPILOGUE_WARPS / 4);
+        const int col_begin = ((warp - 2) >> 2) * kColsPerWarp;
         int acc = 0;
         unsigned acc_phase = 0;
         bool ok = true;
@@ -362,18 +366,26 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
             const bool vec4 = (ld & 3) == 0 && (((unsigned long long)dst) & 15) == 0;
             const bool vec16 = (p.ldc16 & 7) == 0 && (((unsigned long long)p.c16) & 15) == 0;
 #pragma unroll 1
-            for (int chunk = 0; chunk < MC_TC_BN / 32; ++chunk) {
-                const int col0 = n0 + chunk * 32;
+            for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {
+                const int col_local = col_begin + chunk * 32;
+                const int col0 = n0 + col_local;
                 if (col0 >= p.n) break;  // warp-uniform
                 unsigned v[32];
-                mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * MC_TC_BN + chunk * 32), v);
+                mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * MC_TC_BN + col_local), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (row < p.m) {
                     float f[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        f[j] = __uint_as_float(v[j]);
-                        if (!partial && col0 + j < p.n) f[j] = mc_epilogue(f[j], (unsigned)row, (unsigned)(col0 + j), epi);
+                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                    if (!partial) {
+                        if (col0 + 32 <= p.n) {
+                            mc_epilogue32(f, (unsigned)row, (unsigned)col0, epi);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (col0 + j < p.n) f[j] = mc_epilogue(f[j], (unsigned)row, (unsigned)(col0 + j), epi);
+                            }
+                        }
                     }
                     if (dst != nullptr) {
                         float* out = dst + (long long)row * ld + col0;
