@@ -47,6 +47,13 @@ WORKLOADS = {
     "c5_f16": ("c5_mlp_stack", {"B": 65536, "D": 2048}, "tensor_core_f16", "B", "flops", "normal"),
     "c5_bf16": ("c5_mlp_stack", {"B": 65536, "D": 2048}, "tensor_core_bf16", "B", "flops", "normal"),
 }
+# The rest of the C4 sweep: squares, skinny-M and tall-K shapes, per 16-bit format.
+for _fmt in ("bf16", "f16"):
+    for _s in (1024, 2048, 4096, 16384):
+        WORKLOADS[f"c4_{_fmt}_{_s}"] = ("c4_matmul", {"M": _s, "N": _s, "K": _s}, f"tensor_core_{_fmt}", None, "flops", "uniform")
+    WORKLOADS[f"c4_{_fmt}_m16"] = ("c4_matmul", {"M": 16, "N": 8192, "K": 8192}, f"tensor_core_{_fmt}", None, "flops", "uniform")
+    WORKLOADS[f"c4_{_fmt}_m128"] = ("c4_matmul", {"M": 128, "N": 8192, "K": 8192}, f"tensor_core_{_fmt}", None, "flops", "uniform")
+    WORKLOADS[f"c4_{_fmt}_tallk"] = ("c4_matmul", {"M": 1024, "N": 1024, "K": 65536}, f"tensor_core_{_fmt}", None, "flops", "uniform")
 DTYPES = {"auto": "f32", "tensor_core_tf32": "tf32", "tensor_core_bf16": "bf16", "tensor_core_f16": "f16"}
 
 
@@ -270,21 +277,38 @@ def main():
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
-        events = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        # A working set that fits the 126 MB L2 would be served from it on every repeat: then each step is
+        # timed on its own and a 256 MiB buffer is overwritten between steps to flush the cache.
+        flush_l2 = exe.arena_bytes < (256 << 20)
         count0 = mc.lib().mcd_launch_count()
-        events[0].record(stream)
-        for i in range(steps):
-            exe.enqueue(stream.cuda_stream)
-            events[i + 1].record(stream)
-        torch.cuda.synchronize()
+        if flush_l2:
+            scrub = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+            starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+            stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+            with torch.cuda.stream(stream):
+                for i in range(steps):
+                    scrub.fill_(i & 0xFF)
+                    starts[i].record(stream)
+                    exe.enqueue(stream.cuda_stream)
+                    stops[i].record(stream)
+            torch.cuda.synchronize()
+            step_ms = [starts[i].elapsed_time(stops[i]) for i in range(steps)]
+        else:
+            events = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+            events[0].record(stream)
+            for i in range(steps):
+                exe.enqueue(stream.cuda_stream)
+                events[i + 1].record(stream)
+            torch.cuda.synchronize()
+            step_ms = [events[i].elapsed_time(events[i + 1]) for i in range(steps)]
         count1 = mc.lib().mcd_launch_count()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         clocks = sampler.stop() if rank == 0 else None
         exe.synchronize()  # also surfaces a kernel that gave up a bounded wait
-        total_ms = events[0].elapsed_time(events[-1])
-        per_step = sorted(events[i].elapsed_time(events[i + 1]) for i in range(steps))
+        total_ms = float(sum(step_ms)) if flush_l2 else events[0].elapsed_time(events[-1])
+        per_step = sorted(step_ms)
         t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
         w = torch.tensor([float(work_rank)], dtype=torch.float64, device="cuda")
         if world > 1:
@@ -349,7 +373,8 @@ def main():
             "dtype": DTYPES[matmul], "data": "synthetic",
             "config": {"workload": workload, "graph": name, "dims": dims, "per_rank_dims": my_dims, "matmul": matmul,
                        "matmul_kernels": exe.matmul_kernels, "kernel_launches_per_step": launches_per_step,
-                       "l2": "inputs and outputs of a step exceed the 126 MB L2" if work_rank > 3e8 or kind == "flops" else "small",
+                       "l2": "flushed between steps (256 MiB overwrite), steps timed one by one" if flush_l2
+                       else "not flushed: the tensors a step streams exceed the 126 MB L2",
                        "inputs": f"{dist_name} (splitmix64 stream, seed 1 + 1000*rank)"},
             "e2e": e2e, "gpu_launches": int(count1 - count0), "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
             "jit_compile_ms": exe.jit_compile_ms, "arena_bytes": exe.arena_bytes,
