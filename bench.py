@@ -336,7 +336,9 @@ def main():
             e2e = {"value": work_all * e2e_steps / float(tt.item()) / denom, "unit": "GB/s" if kind == "bytes" else "TFLOP/s",
                    "h2d_bytes_per_step": int(sum(a.numel() * 4 for a in pinned_in)),
                    "d2h_bytes_per_step": int(sum(a.numel() * 4 for a in pinned_out)), "steps": e2e_steps,
-                   "timing": "host wall clock around mc_run (it synchronizes), max over ranks"}
+                   "timing": "host wall clock around mc_run (it synchronizes), max over ranks",
+                   "path": "mc_run on pinned host buffers; a graph that only streams (every input read once, by generated "
+                           "elementwise kernels) reads and writes them in place over PCIe, any other graph is copied in and out"}
 
         peaks = measured_peaks()
         median_ms = per_step[len(per_step) // 2]

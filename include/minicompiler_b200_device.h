@@ -58,6 +58,9 @@ MCD_API int mcd_memset(void* ptr, int byte, size_t bytes, void* stream);
 MCD_API int mcd_copy_h2d(void* dst, const void* src, size_t bytes, void* stream);
 MCD_API int mcd_copy_d2h(void* dst, const void* src, size_t bytes, void* stream);
 MCD_API int mcd_copy_d2d(void* dst, const void* src, size_t bytes, void* stream);
+/* The device-side address of pinned, mapped host memory (cudaHostAlloc / cudaHostRegister), for kernels that
+ * read or write caller memory in place; non-zero when `host` is pageable or not addressable by the GPU. */
+MCD_API int mcd_host_device_pointer(const void* host, void** device_alias);
 MCD_API int mcd_host_register(void* ptr, size_t bytes);   /* pin caller memory (optional fast path) */
 MCD_API int mcd_host_unregister(void* ptr);
 MCD_API int mcd_stream_create(void** stream);
@@ -67,6 +70,7 @@ MCD_API int mcd_device_synchronize(void);
 MCD_API int mcd_event_create(void** event);
 MCD_API int mcd_event_destroy(void* event);
 MCD_API int mcd_event_record(void* event, void* stream);
+MCD_API int mcd_stream_wait_event(void* stream, void* event); /* later work on `stream` waits for `event` */
 MCD_API int mcd_event_elapsed_ms(void* start, void* stop, float* ms); /* waits for `stop` */
 
 /* -------------------------------------------------------- run-time kernels
@@ -82,6 +86,13 @@ MCD_API int mcd_jit_occupancy(void* function, int block_threads, size_t dynamic_
 MCD_API int mcd_jit_set_dynamic_smem(void* function, size_t bytes);
 MCD_API int mcd_launch(void* function, unsigned grid_x, unsigned grid_y, unsigned grid_z, unsigned block_x,
                        size_t dynamic_smem, void* stream, void** params);
+/* Launch-list replay (the reference names CUDA-graph replay of enqueue as its next step, README.md:554-556).
+ * Between begin and end every launch issued on `stream` through this layer is recorded instead of run;
+ * end returns an executable graph that mcd_graph_launch replays on any stream of the same device. */
+MCD_API int mcd_graph_begin_capture(void* stream);
+MCD_API int mcd_graph_end_capture(void* stream, void** graph_exec);
+MCD_API int mcd_graph_launch(void* graph_exec, void* stream);
+MCD_API int mcd_graph_destroy(void* graph_exec);
 /* Number of kernel launches issued through this layer by the calling process. */
 MCD_API unsigned long long mcd_launch_count(void);
 

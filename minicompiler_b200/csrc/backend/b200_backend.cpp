@@ -38,6 +38,8 @@ struct Launch {
     unsigned grid = 0;
     unsigned count = 0;
     std::vector<void*> pointers;
+    std::vector<char> advances;  // per pointer: 1 when it walks the tensor element by element (output, same-size inputs)
+    bool vectorized = false;
     std::vector<void*> params;
     // Matmul
     mcd_gemm_args gemm{};
@@ -61,6 +63,11 @@ public:
 
     ~B200Executable() override {
         if (arena_ != nullptr || stream_ != nullptr) mcd_set_device(options_.device);
+        if (replay_ != nullptr) mcd_graph_destroy(replay_);
+        for (void* e : slice_in_) mcd_event_destroy(e);
+        for (void* e : slice_done_) mcd_event_destroy(e);
+        if (copy_in_ != nullptr) mcd_stream_destroy(copy_in_);
+        if (copy_out_ != nullptr) mcd_stream_destroy(copy_out_);
         if (stream_ != nullptr) mcd_stream_destroy(stream_);
         if (arena_ != nullptr) mcd_free(arena_);
     }
@@ -98,6 +105,9 @@ public:
             return Error{"expected " + std::to_string(graph_.inputs().size()) + " input and " +
                          std::to_string(graph_.outputs().size()) + " output buffers"};
         }
+        bool done = false;
+        MC_TRY(run_on_host_memory(inputs, outputs, &done));
+        if (done) return Status();
         MC_TRY(upload_inputs(inputs));
         MC_TRY(enqueue(nullptr));
         return download_outputs(outputs);
@@ -120,6 +130,10 @@ public:
 
     Status enqueue(void* stream) override {
         void* s = stream != nullptr ? stream : stream_;
+        if (replay_ != nullptr) {
+            MCD_TRY(mcd_graph_launch(replay_, s));
+            return Status();
+        }
         for (const std::unique_ptr<Launch>& l : launches_) MC_TRY(issue(*l, s));
         return Status();
     }
@@ -182,6 +196,148 @@ public:
 
 private:
     B200Executable(const Graph& graph, const CudaOptions& options) : graph_(graph), options_(options) {}
+
+    // run() without staging copies, for graphs that only stream: when every step is a generated elementwise
+    // kernel, every graph input is read by exactly one of them and every output is written by one and read by
+    // none, and the caller's buffers are pinned host memory the GPU can address, the kernels read the inputs
+    // and write the outputs in place over PCIe. Both directions then move at once and each byte crosses the bus
+    // once, instead of copy-in, compute, copy-out one after the other. Sets *done when it ran.
+    Status run_on_host_memory(const std::vector<const float*>& inputs, const std::vector<float*>& outputs, bool* done) {
+        *done = false;
+        if (!streams_only_) return Status();
+        std::vector<void*> in_alias(inputs.size()), out_alias(outputs.size());
+        for (std::size_t k = 0; k < inputs.size(); ++k) {
+            if (mcd_host_device_pointer(inputs[k], &in_alias[k]) != 0) return Status();
+        }
+        for (std::size_t k = 0; k < outputs.size(); ++k) {
+            if (mcd_host_device_pointer(outputs[k], &out_alias[k]) != 0) return Status();
+        }
+        MCD_TRY(mcd_set_device(options_.device));
+        if (pipeline_elements_ > 0) {
+            MC_TRY(run_pipelined(inputs, outputs));
+            *done = true;
+            return Status();
+        }
+        for (const std::unique_ptr<Launch>& l : launches_) {
+            std::vector<void*> pointers = l->pointers;
+            for (void*& ptr : pointers) {
+                for (std::size_t k = 0; k < inputs.size(); ++k) {
+                    if (ptr == address(graph_.inputs()[k], kRepF32)) ptr = in_alias[k];
+                }
+                for (std::size_t k = 0; k < outputs.size(); ++k) {
+                    if (ptr == address(graph_.outputs()[k], kRepF32)) ptr = out_alias[k];
+                }
+            }
+            std::vector<void*> params;
+            for (void*& ptr : pointers) params.push_back(&ptr);
+            unsigned count = l->count;
+            params.push_back(&count);
+            MCD_TRY(mcd_launch(l->function, l->grid, 1, 1, kElementwiseBlock, 0, stream_, params.data()));
+        }
+        MCD_TRY(mcd_stream_synchronize(stream_));
+        *done = true;
+        return Status();
+    }
+
+    // The streaming graph in slices of rows, three stages deep: while slice i is computed, slice i+1 comes in
+    // on one copy engine and slice i-1 goes out on the other, so both directions of the bus stay busy.
+    // Applies when every tensor the kernels walk has the same element count (pipeline_elements_).
+    Status run_pipelined(const std::vector<const float*>& inputs, const std::vector<float*>& outputs) {
+        const std::size_t total = pipeline_elements_;
+        const std::size_t slices = kPipelineSlices;
+        const std::size_t per = ((total + slices - 1) / slices + 1023) / 1024 * 1024;  // whole 128-bit groups, whole periods
+        for (std::size_t c = 0; c * per < total; ++c) {
+            const std::size_t first = c * per;
+            const std::size_t count = std::min(per, total - first);
+            for (std::size_t k = 0; k < inputs.size(); ++k) {
+                const NodeId id = graph_.inputs()[k];
+                const std::size_t n = graph_.node(id).type.num_elements();
+                if (n == total) {
+                    MCD_TRY(mcd_copy_h2d(address(id, kRepF32) + first * 4, inputs[k] + first, count * 4, copy_in_));
+                } else if (c == 0) {
+                    MCD_TRY(mcd_copy_h2d(address(id, kRepF32), inputs[k], n * 4, copy_in_));
+                }
+            }
+            MCD_TRY(mcd_event_record(slice_in_[c], copy_in_));
+            MCD_TRY(mcd_stream_wait_event(stream_, slice_in_[c]));
+            for (const std::unique_ptr<Launch>& l : launches_) {
+                std::vector<void*> pointers = l->pointers;
+                for (std::size_t i = 0; i < pointers.size(); ++i) {
+                    if (l->advances[i]) pointers[i] = static_cast<char*>(pointers[i]) + first * 4;
+                }
+                std::vector<void*> params;
+                for (void*& ptr : pointers) params.push_back(&ptr);
+                unsigned n = static_cast<unsigned>(l->vectorized ? count / 4 : count);
+                params.push_back(&n);
+                const std::size_t per_block = static_cast<std::size_t>(kElementwiseBlock) * options_.eltwise_unroll;
+                const unsigned grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min<std::size_t>(l->grid, (n + per_block - 1) / per_block)));
+                MCD_TRY(mcd_launch(l->function, grid, 1, 1, kElementwiseBlock, 0, stream_, params.data()));
+            }
+            MCD_TRY(mcd_event_record(slice_done_[c], stream_));
+            MCD_TRY(mcd_stream_wait_event(copy_out_, slice_done_[c]));
+            for (std::size_t k = 0; k < outputs.size(); ++k) {
+                const NodeId id = graph_.outputs()[k];
+                MCD_TRY(mcd_copy_d2h(outputs[k] + first, address(id, kRepF32) + first * 4, count * 4, copy_out_));
+            }
+        }
+        MCD_TRY(mcd_stream_synchronize(copy_out_));
+        MCD_TRY(mcd_stream_synchronize(stream_));
+        return Status();
+    }
+
+    // Element count shared by every walked tensor when the graph can run in row slices, else 0.
+    std::size_t pipeline_elements() const {
+        if (!streams_only_ || options_.host_io != 1) return 0;
+        std::size_t total = 0;
+        for (const std::unique_ptr<Launch>& l : launches_) {
+            const std::size_t n = static_cast<std::size_t>(l->count) * (l->vectorized ? 4 : 1);
+            if (total == 0) total = n;
+            if (n != total || (l->vectorized ? n % 4 != 0 : false)) return 0;
+        }
+        // Operands that repeat (bias rows) must repeat whole within a slice: slices are multiples of 1024 elements.
+        // Anything whose index depends on the position in the whole tensor (a [M,1] column, say) rules slicing out.
+        for (const Step& s : lowered_.steps) {
+            const Shape& out_shape = graph_.node(s.result).type.shape;
+            for (NodeId in : s.inputs) {
+                const Access a = classify_access(graph_.node(in).type.shape, out_shape);
+                if (a.kind == AccessKind::General) return 0;
+                if (a.kind == AccessKind::Periodic && (a.period > 1024 || 1024 % a.period != 0)) return 0;
+            }
+        }
+        return total >= (std::size_t{1} << 22) ? total : 0;  // below 16 MiB a slice is too small to be worth a stage
+    }
+
+    // Whether run_on_host_memory applies to this graph at all (decided once, at compile time).
+    bool graph_only_streams() const {
+        if (options_.host_io == 0) return false;
+        std::vector<int> reads(graph_.num_nodes(), 0);
+        for (const Step& s : lowered_.steps) {
+            if (s.kind != Step::Kind::Elementwise) return false;
+            if (s.write_half != HalfKind::None) return false;
+            std::vector<NodeId> seen;
+            for (NodeId in : s.inputs) {
+                if (std::find(seen.begin(), seen.end(), in) != seen.end()) continue;
+                seen.push_back(in);
+                ++reads[static_cast<std::size_t>(in)];
+                // A broadcast operand would cross the bus once per repetition: only same-size or one-element inputs.
+                const std::size_t count = graph_.node(in).type.num_elements();
+                if (graph_.node(in).op == OpKind::Input && count != 1 &&
+                    count != graph_.node(s.result).type.num_elements()) {
+                    return false;
+                }
+            }
+        }
+        for (const std::vector<Recast>& after : lowered_.after_step) {
+            if (!after.empty()) return false;
+        }
+        for (NodeId in : graph_.inputs()) {
+            if (reads[static_cast<std::size_t>(in)] != 1 || graph_.is_output(in)) return false;
+        }
+        for (NodeId out : graph_.outputs()) {
+            if (!is_compute(graph_.node(out).op) || reads[static_cast<std::size_t>(out)] != 0) return false;
+        }
+        return !lowered_.steps.empty();
+    }
 
     char* address(NodeId id, Rep rep) const {
         const std::size_t slot = static_cast<std::size_t>(id) * kNumReps + static_cast<std::size_t>(rep);
@@ -329,6 +485,39 @@ private:
             }
             for (const Recast& rc : lowered_.after_step[i]) launches_.push_back(std::make_unique<Launch>(make_recast(rc)));
         }
+        // Every buffer address is fixed for the life of the executable, so the launch list can be recorded
+        // once and replayed: one graph launch per enqueue instead of one driver call (and, for tensor-core
+        // matmuls, two tensor-map encodings) per kernel. The list runs once for real first, so that one-time
+        // kernel set-up does not happen inside the recording.
+        streams_only_ = graph_only_streams();
+        pipeline_elements_ = pipeline_elements();
+        if (pipeline_elements_ > 0) {
+            MCD_TRY(mcd_stream_create(&copy_in_));
+            MCD_TRY(mcd_stream_create(&copy_out_));
+            slice_in_.assign(kPipelineSlices, nullptr);
+            slice_done_.assign(kPipelineSlices, nullptr);
+            for (std::size_t c = 0; c < kPipelineSlices; ++c) {
+                MCD_TRY(mcd_event_create(&slice_in_[c]));
+                MCD_TRY(mcd_event_create(&slice_done_[c]));
+            }
+        }
+        if (options_.replay_graph && launches_.size() >= 2) {
+            for (const std::unique_ptr<Launch>& l : launches_) MC_TRY(issue(*l, stream_));
+            MCD_TRY(mcd_stream_synchronize(stream_));
+            MCD_TRY(mcd_graph_begin_capture(stream_));
+            Status recorded;
+            for (const std::unique_ptr<Launch>& l : launches_) {
+                recorded = issue(*l, stream_);
+                if (!recorded.ok()) break;
+            }
+            void* graph = nullptr;
+            const int rc = mcd_graph_end_capture(stream_, &graph);
+            if (!recorded.ok()) return recorded;
+            if (rc != 0) return device_error("mcd_graph_end_capture");
+            replay_ = graph;
+            MCD_TRY(mcd_memset(status_word(), 0, kAlign, stream_));
+            MCD_TRY(mcd_stream_synchronize(stream_));
+        }
         return Status();
     }
 
@@ -365,9 +554,19 @@ private:
         const std::size_t wanted = (launch->count + per_block - 1) / per_block;
         const std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
         launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(wanted, resident)));
-        if (kernel.has_f32_out) launch->pointers.push_back(address(step.result, kRepF32));
-        if (kernel.has_half_out) launch->pointers.push_back(address(step.result, kRepHalf));
-        for (NodeId in : step.inputs) launch->pointers.push_back(address(in, kRepF32));
+        launch->vectorized = kernel.vectorized;
+        if (kernel.has_f32_out) {
+            launch->pointers.push_back(address(step.result, kRepF32));
+            launch->advances.push_back(1);
+        }
+        if (kernel.has_half_out) {
+            launch->pointers.push_back(address(step.result, kRepHalf));
+            launch->advances.push_back(1);
+        }
+        for (NodeId in : step.inputs) {
+            launch->pointers.push_back(address(in, kRepF32));
+            launch->advances.push_back(graph_.node(in).type.num_elements() == n ? 1 : 0);
+        }
         for (void*& p : launch->pointers) launch->params.push_back(&p);
         launch->params.push_back(&launch->count);
         launches_.push_back(std::move(launch));
@@ -455,6 +654,14 @@ private:
     LoweredGraph lowered_;
     void* stream_ = nullptr;
     void* arena_ = nullptr;
+    void* replay_ = nullptr;
+    bool streams_only_ = false;
+    static constexpr std::size_t kPipelineSlices = 48;
+    std::size_t pipeline_elements_ = 0;
+    void* copy_in_ = nullptr;
+    void* copy_out_ = nullptr;
+    std::vector<void*> slice_in_;
+    std::vector<void*> slice_done_;
     std::size_t arena_bytes_ = 0;
     std::size_t constants_bytes_ = 0;
     std::size_t status_offset_ = 0;

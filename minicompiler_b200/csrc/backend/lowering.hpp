@@ -68,6 +68,11 @@ struct CudaOptions {
     unsigned eltwise_unroll = 4;
     bool streaming_hints = true;
     int gemm_variant = 0;
+    bool replay_graph = true;       // record the launch list once and replay it as a CUDA graph (2+ launches)
+    // run() on pinned caller memory for graphs that only stream: 0 = always copy in / run / copy out;
+    // 1 = slices pipelined over both copy engines when the graph allows it, else kernels on host memory in place;
+    // 2 = kernels on host memory in place only.
+    int host_io = 1;
     bool eltwise_fmad = false;      // let the compiler contract a*b+c in generated kernels (not bit-exact vs the CPU)
     // Cap on resident blocks per SM for the one-wave grid (0 = whatever occupancy allows). On B200 four
     // 256-thread blocks with four 128-bit loads in flight per thread stream faster than eight (6.1 vs

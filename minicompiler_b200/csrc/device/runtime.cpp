@@ -299,6 +299,19 @@ int mcd_copy_d2d(void* dst, const void* src, size_t bytes, void* stream) {
     return check_rt(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)),
                     "cudaMemcpyAsync(device to device)");
 }
+int mcd_host_device_pointer(const void* host, void** device_alias) {
+    *device_alias = nullptr;
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, host) != cudaSuccess) {
+        cudaGetLastError();
+        return fail("mcd_host_device_pointer: not a CUDA-visible address");
+    }
+    if (attr.type != cudaMemoryTypeHost || attr.devicePointer == nullptr) {
+        return fail("mcd_host_device_pointer: the memory is not pinned and mapped");
+    }
+    *device_alias = attr.devicePointer;
+    return 0;
+}
 int mcd_host_register(void* ptr, size_t bytes) {
     return check_rt(cudaHostRegister(ptr, bytes, cudaHostRegisterDefault), "cudaHostRegister");
 }
@@ -324,6 +337,9 @@ int mcd_event_create(void** event) {
 }
 int mcd_event_destroy(void* event) {
     return event == nullptr ? 0 : check_rt(cudaEventDestroy(static_cast<cudaEvent_t>(event)), "cudaEventDestroy");
+}
+int mcd_stream_wait_event(void* stream, void* event) {
+    return check_rt(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(event), 0), "cudaStreamWaitEvent");
 }
 int mcd_event_record(void* event, void* stream) {
     return check_rt(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)), "cudaEventRecord");
@@ -408,6 +424,53 @@ int mcd_launch(void* function, unsigned grid_x, unsigned grid_y, unsigned grid_z
     return check_drv(drv->LaunchKernel(static_cast<CUfunction>(function), grid_x, grid_y, grid_z, block_x, 1, 1,
                                        static_cast<unsigned>(dynamic_smem), static_cast<CUstream>(stream), params, nullptr),
                      "cuLaunchKernel");
+}
+
+// ------------------------------------------------------------ graph replay
+
+namespace {
+struct GraphExec {
+    cudaGraphExec_t exec = nullptr;
+    unsigned long long kernels = 0;
+};
+thread_local unsigned long long g_capture_start = 0;
+}  // namespace
+
+int mcd_graph_begin_capture(void* stream) {
+    g_capture_start = g_launches.load();
+    return check_rt(cudaStreamBeginCapture(static_cast<cudaStream_t>(stream), cudaStreamCaptureModeThreadLocal),
+                    "cudaStreamBeginCapture");
+}
+
+int mcd_graph_end_capture(void* stream, void** graph_exec) {
+    *graph_exec = nullptr;
+    cudaGraph_t graph = nullptr;
+    if (int rc = check_rt(cudaStreamEndCapture(static_cast<cudaStream_t>(stream), &graph), "cudaStreamEndCapture")) return rc;
+    auto* ge = new GraphExec();
+    ge->kernels = g_launches.load() - g_capture_start;
+    g_launches.store(g_capture_start);  // recorded, not run
+    const int rc = check_rt(cudaGraphInstantiate(&ge->exec, graph, 0), "cudaGraphInstantiate");
+    cudaGraphDestroy(graph);
+    if (rc != 0) {
+        delete ge;
+        return rc;
+    }
+    *graph_exec = ge;
+    return 0;
+}
+
+int mcd_graph_launch(void* graph_exec, void* stream) {
+    auto* ge = static_cast<GraphExec*>(graph_exec);
+    g_launches.fetch_add(ge->kernels, std::memory_order_relaxed);
+    return check_rt(cudaGraphLaunch(ge->exec, static_cast<cudaStream_t>(stream)), "cudaGraphLaunch");
+}
+
+int mcd_graph_destroy(void* graph_exec) {
+    auto* ge = static_cast<GraphExec*>(graph_exec);
+    if (ge == nullptr) return 0;
+    const int rc = check_rt(cudaGraphExecDestroy(ge->exec), "cudaGraphExecDestroy");
+    delete ge;
+    return rc;
 }
 
 // Compile-only entry point (no GPU needed): used by tests and `mcc --emit-cuda --check`.

@@ -385,3 +385,30 @@ def test_large_matmul_sampled_and_checksum(mc, oracle):
         scale = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64).sum(axis=1)
         rel = np.max(np.abs(got.astype(np.float64).sum(axis=1) - rowsum) / scale)
         assert rel <= (2 * u + 4096 * U32 * 2), f"{name}: row-sum identity off by {rel:.3e}"
+
+
+def test_run_on_pinned_host_memory_equals_run_with_copies(mc, oracle):
+    """mc_run on pinned buffers lets a streaming graph read and write caller memory in place (no staging
+    copies); the results must be the ones the copying path gives, bit for bit."""
+    torch = _torch()
+    path = mc.graph_path("c2_gelu_chain")
+    dims = {"M": 1000, "N": 1028}
+    x = oracle.normal_values(1000 * 1028, 3)
+    with mc.CompiledGraph(path, dims=dims, options={"host_io": 0}) as exe:
+        want = exe.run([x])[0]
+    pin_in = torch.from_numpy(x.copy()).pin_memory()
+    pin_out = torch.full((x.size,), float("nan"), dtype=torch.float32).pin_memory()
+    with mc.CompiledGraph(path, dims=dims) as exe:
+        exe.run_ptrs([pin_in.data_ptr()], [pin_out.data_ptr()])
+        assert np.array_equal(pin_out.numpy(), want)
+        assert np.array_equal(exe.run([x])[0], want)  # pageable memory: falls back to copies
+    # two chained kernels (no fusion): the intermediate stays on the device, the ends stream from/to the host
+    text = "input a : f32[512, 64]\ninput b : f32[512, 64]\ninput c : f32[512, 64]\nt = mul a, b\nu = exp t\ny = add u, c\noutput y"
+    g, ins = oracle_inputs(oracle, text, seed=4)
+    with mc.CompiledGraph(text=text, passes="none", options={"host_io": 0}) as exe:
+        want = exe.run(ins)[0]
+    pins = [torch.from_numpy(a.reshape(-1).copy()).pin_memory() for a in ins]
+    out = torch.empty(512 * 64, dtype=torch.float32).pin_memory()
+    with mc.CompiledGraph(text=text, passes="none") as exe:
+        exe.run_ptrs([p.data_ptr() for p in pins], [out.data_ptr()])
+    assert np.array_equal(out.numpy(), want)
