@@ -212,6 +212,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--also", default="", help="comma-separated extra workloads measured briefly (N=1 only)")
+    ap.add_argument("--options", default="", help="extra compile options, e.g. gemm_variant=2,fuse_epilogue=0 (for A/B measurements)")
     ap.add_argument("--dims", default="", help="override dims of the workload, e.g. M=4096,N=8192 (for small profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -245,7 +246,10 @@ def main():
             dims_str, row_offset, rows = mc.shard_dims(path, dims, batch_dim, rank, world)
             my_dims = {k: int(v) for k, v in (kv.split("=") for kv in dims_str.split(","))}
             scaling = "strong"
-        exe = mc.CompiledGraph(path, dims=my_dims, options={"device": local_rank, "matmul": matmul})
+        compile_options = {"device": local_rank, "matmul": matmul}
+        if args.options:
+            compile_options |= dict(kv.split("=") for kv in args.options.split(","))
+        exe = mc.CompiledGraph(path, dims=my_dims, options=compile_options)
         if world > 1:
             # Constants are generated identically on every rank; one NCCL broadcast over NVLink makes rank 0's
             # copy the one everybody uses (and is the only collective on this path).

@@ -298,10 +298,15 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     p.idesc = instruction_descriptor(a->arith, b_k_major);
     p.k_blocks_per_split = per;
     p.splits = splits;
+    // Tiles that do not fill the last wave of CTAs are cut in two when both halves of all of them fit in one wave.
+    const int sms = sm_count_of_current_device();
+    const int all_tiles = ((a->m + MC_TC_BM - 1) / MC_TC_BM) * ((a->n + MC_TC_BN - 1) / MC_TC_BN);
+    const int tail = all_tiles % sms;
+    p.half_tiles = (splits == 1 && (a->variant & 2) == 0 && tail > 0 && 2 * tail <= sms) ? tail : 0;
     McEpilogueArgs epi = epilogue_args(a);
 
-    const int tiles = ((a->m + MC_TC_BM - 1) / MC_TC_BM) * ((a->n + MC_TC_BN - 1) / MC_TC_BN) * splits;
-    const unsigned grid = static_cast<unsigned>(std::max(1, std::min(tiles, sm_count_of_current_device())));
+    const int tiles = (all_tiles + p.half_tiles) * splits;
+    const unsigned grid = static_cast<unsigned>(std::max(1, std::min(tiles, sms)));
 
     if (a->function != nullptr && splits == 1) {
         void* params[] = {&map_a, &map_b, &p, &epi};

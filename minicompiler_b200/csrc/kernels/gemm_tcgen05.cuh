@@ -58,6 +58,7 @@ struct McTcParams {
     unsigned idesc;
     int k_blocks_per_split;  // K blocks (of 128 bytes) per work item
     int splits;
+    int half_tiles;  // the last `half_tiles` tiles are each issued as two 128-column work items (splits == 1 only)
 };
 
 __device__ __forceinline__ unsigned mc_smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -171,10 +172,19 @@ __device__ __forceinline__ unsigned long long mc_smem_desc(unsigned addr, unsign
     return d;
 }
 
-// Work item -> (m block, n block, k split), rastered in bands of MC_TC_RASTER m-blocks.
-__device__ __forceinline__ void mc_tc_decode(int item, int tiles_m, int tiles_n, int splits, int& mb, int& nb, int& split) {
+// Work item -> (m block, n block, k split, column half), rastered in bands of MC_TC_RASTER m-blocks.
+// When the tiles do not fill the last wave of CTAs, the tiles of that wave are cut into two 128-column
+// halves (half = 0 / 1, otherwise -1), so that twice as many SMs share the tail.
+__device__ __forceinline__ void mc_tc_decode(int item, int tiles_m, int tiles_n, int splits, int half_tiles, int& mb, int& nb,
+                                             int& split, int& half) {
     split = item % splits;
-    const int tile = item / splits;
+    int tile = item / splits;
+    half = -1;
+    const int whole = tiles_m * tiles_n - half_tiles;
+    if (half_tiles > 0 && tile >= whole) {
+        half = (tile - whole) & 1;
+        tile = whole + ((tile - whole) >> 1);
+    }
     const int band_tiles = MC_TC_RASTER * tiles_n;
     const int band = tile / band_tiles;
     const int first_m = band * MC_TC_RASTER;
@@ -212,7 +222,7 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
     const int tiles_m = (p.m + MC_TC_BM - 1) / MC_TC_BM;
     const int tiles_n = (p.n + MC_TC_BN - 1) / MC_TC_BN;
     const int k_blocks = (p.k + kBlockK - 1) / kBlockK;
-    const int items = tiles_m * tiles_n * p.splits;
+    const int items = (tiles_m * tiles_n + p.half_tiles) * p.splits;
 
     if (threadIdx.x == 0) {
         abort_flag_storage = 0;
@@ -245,8 +255,8 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
             int issued = 0;
             bool ok = true;
             for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
-                int mb, nb, split;
-                mc_tc_decode(item, tiles_m, tiles_n, p.splits, mb, nb, split);
+                int mb, nb, split, half;
+                mc_tc_decode(item, tiles_m, tiles_n, p.splits, p.half_tiles, mb, nb, split, half);
                 const int kb_begin = split * p.k_blocks_per_split;
                 const int kb_end = min(k_blocks, kb_begin + p.k_blocks_per_split);
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
@@ -304,14 +314,16 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
             unsigned acc_phase = 0;
             bool ok = true;
             for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
-                int mb, nb, split;
-                mc_tc_decode(item, tiles_m, tiles_n, p.splits, mb, nb, split);
+                int mb, nb, split, half;
+                mc_tc_decode(item, tiles_m, tiles_n, p.splits, p.half_tiles, mb, nb, split, half);
                 const int kb_begin = split * p.k_blocks_per_split;
                 const int kb_end = min(k_blocks, kb_begin + p.k_blocks_per_split);
                 ok = mc_mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, MC_TC_ERR_MMA);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned tmem_d = tmem_base + (unsigned)(acc * MC_TC_BN);
+                // N field of the instruction descriptor (bits 17-22, N >> 3): 128 for a half tile.
+                const unsigned idesc = half < 0 ? p.idesc : ((p.idesc & ~(0x3Fu << 17)) | ((unsigned)(MC_TC_BN / 2 >> 3) << 17));
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
                     ok = mc_mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, MC_TC_ERR_MMA);
                     if (!ok) break;
@@ -322,13 +334,16 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
                     const unsigned long long desc_a = mc_smem_desc(a_src, 16, 1024);
                     // MN-major B: 128-byte atoms of columns, each holding kBlockK rows; 8-row groups 1024 bytes
                     // apart, atoms kBlockK*128 bytes apart; a K step is kMmaK rows.
-                    const unsigned long long desc_b =
-                        kBIsKMajor ? mc_smem_desc(b_src, 16, 1024) : mc_smem_desc(b_src, kBlockK * 128, 1024);
+                    // A half tile reads its 128 columns out of the same staged 256-column tile: 128 rows further
+                    // on in the K-major form, two column atoms further on in the MN-major form, 16 KB either way.
+                    const unsigned b_half = half == 1 ? (unsigned)(MC_TC_B_BYTES / 2) : 0u;
+                    const unsigned long long desc_b = kBIsKMajor ? mc_smem_desc(b_src + b_half, 16, 1024)
+                                                                 : mc_smem_desc(b_src + b_half, kBlockK * 128, 1024);
                     const unsigned b_step = kBIsKMajor ? 2u : (unsigned)(kMmaK * 128) >> 4;
 #pragma unroll
                     for (int ks = 0; ks < kMmasPerBlock; ++ks) {
                         mc_umma(tmem_d, desc_a + (unsigned long long)(2 * ks), desc_b + (unsigned long long)(b_step * ks),
-                                p.idesc, (kb > kb_begin || ks > 0) ? 1u : 0u, kTf32);
+                                idesc, (kb > kb_begin || ks > 0) ? 1u : 0u, kTf32);
                     }
                     mc_umma_commit(bar_empty + 8 * stage);  // the stage is free once these MMAs have read it
                     if (++stage == MC_TC_STAGES) {
@@ -353,8 +368,8 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
         bool ok = true;
         const bool partial = p.splits > 1;
         for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
-            int mb, nb, split;
-            mc_tc_decode(item, tiles_m, tiles_n, p.splits, mb, nb, split);
+            int mb, nb, split, half;
+            mc_tc_decode(item, tiles_m, tiles_n, p.splits, p.half_tiles, mb, nb, split, half);
             ok = mc_mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, p.status, MC_TC_ERR_EPILOGUE);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -366,12 +381,16 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
             const bool vec4 = (ld & 3) == 0 && (((unsigned long long)dst) & 15) == 0;
             const bool vec16 = (p.ldc16 & 7) == 0 && (((unsigned long long)p.c16) & 15) == 0;
 #pragma unroll 1
-            for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {
-                const int col_local = col_begin + chunk * 32;
-                const int col0 = n0 + col_local;
+            // A whole tile: this warp's half of 256 columns. A half tile: this warp's half of its 128 columns,
+            // which sit in accumulator columns 0..127.
+            const int warp_cols = half < 0 ? kColsPerWarp : kColsPerWarp / 2;
+            const int acc_col_begin = half < 0 ? col_begin : col_begin / 2;
+            const int tile_col_begin = half < 0 ? col_begin : half * (MC_TC_BN / 2) + col_begin / 2;
+            for (int chunk = 0; chunk < warp_cols / 32; ++chunk) {
+                const int col0 = n0 + tile_col_begin + chunk * 32;
                 if (col0 >= p.n) break;  // warp-uniform
                 unsigned v[32];
-                mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * MC_TC_BN + col_local), v);
+                mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * MC_TC_BN + acc_col_begin + chunk * 32), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (row < p.m) {
                     float f[32];
