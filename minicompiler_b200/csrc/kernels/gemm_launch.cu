@@ -20,6 +20,7 @@
 #include "kernels/epilogue.cuh"
 #include "kernels/gemm_f32_simt.cuh"
 #include "kernels/gemm_tcgen05.cuh"
+#include "kernels/gemm_tcgen05_2cta.cuh"
 #include "kernels/splitk_reduce.cuh"
 
 namespace mcd {
@@ -27,6 +28,7 @@ extern std::atomic<unsigned long long> g_launches;
 extern const char* const kSourceEpilogue;
 extern const char* const kSourceGemmF32;
 extern const char* const kSourceGemmTc;
+extern const char* const kSourceGemmTc2;
 extern const char* const kSourceSplitkReduce;
 }  // namespace mcd
 
@@ -251,6 +253,27 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const
                      "cuTensorMapEncodeTiled");
 }
 
+// K blocks and effective K splits of a tensor-core launch.
+int tc_splits(const mcd_gemm_args* a) {
+    const int block_k = a->arith == MCD_GEMM_TF32 ? 32 : 64;
+    const int k_blocks = (a->k + block_k - 1) / block_k;
+    int splits = std::max(1, std::min(a->splits, k_blocks));
+    const int per = (k_blocks + splits - 1) / splits;
+    return (k_blocks + per - 1) / per;
+}
+
+// Whether the launch goes to the SM-pair kernel: unsplit problems whose 256 x 256 pair tiles give every SM pair
+// at least kPairMinWaves tiles; variant bit 8 forces it for any unsplit problem, bit 4 turns it off.
+constexpr int kPairMinWaves = 4;
+bool tc_uses_pairs(const mcd_gemm_args* a) {
+    if (a->arith == MCD_GEMM_F32 || tc_splits(a) != 1 || (a->variant & 4) != 0) return false;
+    if (a->arith == MCD_GEMM_TF32 && a->b_transposed == 0) return false;
+    if ((a->variant & 8) != 0) return true;
+    const long long tiles_m = (a->m + MC_TC_BM - 1) / MC_TC_BM;
+    const long long items = ((tiles_m + 1) / 2) * ((a->n + MC_TC_BN - 1) / MC_TC_BN);
+    return items >= static_cast<long long>(kPairMinWaves) * (sm_count_of_current_device() / 2);
+}
+
 int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     const bool tf32 = a->arith == MCD_GEMM_TF32;
     const int elem = tf32 ? 4 : 2;
@@ -274,8 +297,11 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_a), type, elem, a->a, a->k, a->m, a->lda, block_k, MC_TC_BM)) {
         return rc;
     }
+    const bool pairs = tc_uses_pairs(a);
     if (b_k_major) {
-        if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_b), type, elem, a->b, a->k, a->n, a->ldb, block_k, MC_TC_BN)) {
+        // A CTA of the pair kernel keeps 128 of the tile's 256 columns.
+        if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_b), type, elem, a->b, a->k, a->n, a->ldb, block_k,
+                                pairs ? MC_TC_BN / 2 : MC_TC_BN)) {
             return rc;
         }
     } else {
@@ -304,6 +330,32 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     const int tail = all_tiles % sms;
     p.half_tiles = (splits == 1 && (a->variant & 2) == 0 && tail > 0 && 2 * tail <= sms) ? tail : 0;
     McEpilogueArgs epi = epilogue_args(a);
+
+    if (pairs) {
+        p.half_tiles = 0;
+        p.idesc = (p.idesc & ~(0x1Fu << 24)) | (static_cast<unsigned>(2 * MC_TC_BM >> 4) << 24);  // M = 256 over the pair
+        const int tiles_m = (a->m + MC_TC_BM - 1) / MC_TC_BM;
+        const int items = ((tiles_m + 1) / 2) * ((a->n + MC_TC_BN - 1) / MC_TC_BN);
+        const unsigned pair_grid = 2u * static_cast<unsigned>(std::max(1, std::min(items, sms / 2)));
+        if (a->function != nullptr) {
+            void* params[] = {&map_a, &map_b, &p, &epi};
+            return mcd_launch(a->function, pair_grid, 1, 1, MC_TC_THREADS, MC_TC2_SMEM_BYTES, s, params);
+        }
+        using PairKernel = void (*)(const McTensorMap, const McTensorMap, const McTcParams, const McEpilogueArgs);
+        PairKernel kernel = tf32 ? mc_gemm_tc2_tf32_bk : (b_k_major ? mc_gemm_tc2_h16_bk : mc_gemm_tc2_h16_bmn);
+        static std::atomic<int> pair_configured{0};
+        if (pair_configured.load() == 0) {
+            for (PairKernel kfn : {mc_gemm_tc2_tf32_bk, mc_gemm_tc2_h16_bk, mc_gemm_tc2_h16_bmn}) {
+                if (int rc = check_rt(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_TC2_SMEM_BYTES),
+                                      "cudaFuncSetAttribute(max dynamic shared memory)")) {
+                    return rc;
+                }
+            }
+            pair_configured.store(1);
+        }
+        kernel<<<pair_grid, MC_TC_THREADS, MC_TC2_SMEM_BYTES, s>>>(map_a, map_b, p, epi);
+        return launched("mc_gemm_tc2");
+    }
 
     const int tiles = (all_tiles + p.half_tiles) * splits;
     const unsigned grid = static_cast<unsigned>(std::max(1, std::min(tiles, sms)));
@@ -367,7 +419,7 @@ extern "C" int mcd_gemm_launches(const mcd_gemm_args* a) {
 
 extern "C" const char* mcd_gemm_source(int arith) {
     static const std::string f32 = std::string(kSourceEpilogue) + kSourceGemmF32;
-    static const std::string tc = std::string(kSourceEpilogue) + kSourceGemmTc;
+    static const std::string tc = std::string(kSourceEpilogue) + kSourceGemmTc + kSourceGemmTc2;
     static const std::string reduce = std::string(kSourceEpilogue) + kSourceSplitkReduce;
     if (arith == MCD_GEMM_F32) return f32.c_str();
     if (arith < 0) return reduce.c_str();
@@ -381,11 +433,16 @@ extern "C" const char* mcd_gemm_entry_point(const mcd_gemm_args* a) {
                          a->ldb % 4 == 0;
         return vec ? "mc_gemm_f32_vec" : "mc_gemm_f32_any";
     }
+    if (tc_uses_pairs(a)) {
+        if (a->arith == MCD_GEMM_TF32) return "mc_gemm_tc2_tf32_bk";
+        return a->b_transposed ? "mc_gemm_tc2_h16_bk" : "mc_gemm_tc2_h16_bmn";
+    }
     if (a->arith == MCD_GEMM_TF32) return a->b_transposed ? "mc_gemm_tc_tf32_bk" : "mc_gemm_tc_tf32_bmn";
     return a->b_transposed ? "mc_gemm_tc_h16_bk" : "mc_gemm_tc_h16_bmn";
 }
 
 extern "C" size_t mcd_gemm_dynamic_smem(int arith) {
+    static_assert(MC_TC2_SMEM_BYTES == MC_TC_SMEM_BYTES, "both tensor-core kernels take the same dynamic shared memory");
     return (arith == MCD_GEMM_TF32 || arith == MCD_GEMM_BF16 || arith == MCD_GEMM_F16) ? MC_TC_SMEM_BYTES : 0;
 }
 

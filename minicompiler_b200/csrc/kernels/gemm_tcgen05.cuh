@@ -380,7 +380,6 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
             const long long ld = partial ? (long long)p.n : p.ldc;
             const bool vec4 = (ld & 3) == 0 && (((unsigned long long)dst) & 15) == 0;
             const bool vec16 = (p.ldc16 & 7) == 0 && (((unsigned long long)p.c16) & 15) == 0;
-#pragma unroll 1
             // A whole tile: this warp's half of 256 columns. A half tile: this warp's half of its 128 columns,
             // which sit in accumulator columns 0..127.
             const int warp_cols = half < 0 ? kColsPerWarp : kColsPerWarp / 2;

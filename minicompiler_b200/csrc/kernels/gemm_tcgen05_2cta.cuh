@@ -1,0 +1,361 @@
+// Tensor-core matmul on SM pairs: the same contract as gemm_tcgen05.cuh, for problems large enough
+// to fill the GPU without splitting K. Two CTAs of a cluster (an SM pair) own one 256 x 256 tile of C:
+// each stages its own 128 rows of A and its own 128 columns of B, and the leader CTA issues
+// tcgen05.mma.cta_group::2 (256 x 256 x 16), which reads A and B from both CTAs' shared memory and
+// accumulates each CTA's 128 rows into that CTA's TMEM. Per K block a CTA therefore loads 32 KB instead
+// of 48 KB for the same arithmetic, the ring holds 6 stages instead of 4, and shared-memory read traffic
+// per MMA halves.
+//
+// Protocol (all barriers live at the same shared-memory offsets in both CTAs):
+//   full[s]       leader's only. Armed by the leader's producer with the bytes of BOTH CTAs; the TMA loads of
+//                 both CTAs complete on it (no multicast: every CTA loads only what it keeps).
+//   empty[s]      one per CTA; the leader's tcgen05.commit (cta_group::2, cluster mask 0b11) arrives on both.
+//   tmem_full[a]  one per CTA; same commit form once a tile's last MMA is issued.
+//   tmem_empty[a] leader's only; the 8 epilogue warps of each CTA arrive on it remotely (16 arrivals).
+// Waits are bounded exactly as in the one-CTA kernel; before it returns, every thread of the pair passes a
+// cluster barrier, so neither CTA's shared memory or TMEM goes away under its peer.
+//
+// This text follows gemm_tcgen05.cuh in the same translation unit and uses its helpers.
+
+#define MC_TC2_STAGES 6
+#define MC_TC2_A_BYTES (MC_TC_BM * 128)
+#define MC_TC2_B_BYTES (128 * 128)
+#define MC_TC2_STAGE_BYTES (MC_TC2_A_BYTES + MC_TC2_B_BYTES)
+#define MC_TC2_SMEM_BYTES (MC_TC2_STAGES * MC_TC2_STAGE_BYTES + 1024 + 256)
+
+__device__ __forceinline__ unsigned mc_cluster_ctarank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// The shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ unsigned mc_mapa(unsigned addr, unsigned rank) {
+    unsigned out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+    return out;
+}
+
+__device__ __forceinline__ void mc_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void mc_mbar_arrive_cluster(unsigned cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// TMA load whose completion is counted on a barrier that may sit in the peer CTA of the pair.
+__device__ __forceinline__ void mc_tma_load_2d_pair(unsigned smem_dst, const McTensorMap* map, unsigned bar_cluster_addr, int c0,
+                                                    int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_dst), "l"((unsigned long long)map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void mc_umma_pair(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b, unsigned idesc,
+                                             unsigned accumulate, bool tf32) {
+    if (tf32) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+            "}\n" ::"r"(tmem_d),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+            "}\n" ::"r"(tmem_d),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+// Arrives (once the MMAs issued so far have completed) on the barrier at the same offset in both CTAs.
+__device__ __forceinline__ void mc_umma_commit_pair(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"((unsigned short)3)
+                 : "memory");
+}
+
+template <int kElemBytes, bool kBIsKMajor>
+__device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const McTensorMap& map_b, const McTcParams& p,
+                                                 const McEpilogueArgs& epi) {
+    constexpr int kBlockK = 128 / kElemBytes;
+    constexpr int kMmaK = 32 / kElemBytes;
+    constexpr int kMmasPerBlock = kBlockK / kMmaK;
+    constexpr int kAtomN = 128 / kElemBytes;
+    constexpr bool kTf32 = kElemBytes == 4;
+
+    extern __shared__ unsigned char mc_tc_smem_raw[];
+    const unsigned raw = mc_smem_addr(mc_tc_smem_raw);
+    const unsigned tiles_base = (raw + 1023u) & ~1023u;
+    const unsigned bars_base = tiles_base + MC_TC2_STAGES * MC_TC2_STAGE_BYTES;
+    const unsigned bar_full = bars_base;
+    const unsigned bar_empty = bars_base + 8 * MC_TC2_STAGES;
+    const unsigned bar_tmem_full = bars_base + 16 * MC_TC2_STAGES;
+    const unsigned bar_tmem_empty = bar_tmem_full + 16;
+    __shared__ unsigned tmem_base_slot;
+    __shared__ int abort_flag_storage;
+    volatile int* abort_flag = &abort_flag_storage;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const unsigned rank = mc_cluster_ctarank();
+    const bool leader = rank == 0;
+    const int cluster_id = blockIdx.x >> 1;
+    const int num_clusters = gridDim.x >> 1;
+
+    const int tiles_m = (p.m + MC_TC_BM - 1) / MC_TC_BM;
+    const int pairs_m = (tiles_m + 1) / 2;
+    const int tiles_n = (p.n + MC_TC_BN - 1) / MC_TC_BN;
+    const int k_blocks = (p.k + kBlockK - 1) / kBlockK;
+    const int items = pairs_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        abort_flag_storage = 0;
+        for (int s = 0; s < MC_TC2_STAGES; ++s) {
+            mc_mbar_init(bar_full + 8 * s, 1);
+            mc_mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mc_mbar_init(bar_tmem_full + 8 * a, 1);
+            mc_mbar_init(bar_tmem_empty + 8 * a, 2 * MC_TC_EPILOGUE_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(mc_smem_addr(&tmem_base_slot)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    mc_cluster_sync();  // both CTAs' barriers are initialised before either signals the other's
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_base = tmem_base_slot;
+
+    auto decode = [&](int item, int& mp, int& nb) {
+        constexpr int kBand = MC_TC_RASTER / 2;
+        const int band_tiles = kBand * tiles_n;
+        const int band = item / band_tiles;
+        const int first = band * kBand;
+        const int band_rows = min(kBand, pairs_m - first);
+        const int within = item - band * band_tiles;
+        mp = first + within % band_rows;
+        nb = within / band_rows;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            unsigned phase = 0;
+            int issued = 0;
+            bool ok = true;
+            for (int item = cluster_id; ok && item < items; item += num_clusters) {
+                int mp, nb;
+                decode(item, mp, nb);
+                const int row0 = (2 * mp + (int)rank) * MC_TC_BM;
+                const int col0 = nb * MC_TC_BN + (int)rank * 128;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    ok = mc_mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, MC_TC_ERR_PRODUCER);
+                    if (!ok) break;
+                    const unsigned full_local = bar_full + 8 * stage;
+                    const unsigned full_leader = mc_mapa(full_local, 0);
+                    const unsigned a_dst = tiles_base + stage * MC_TC2_STAGE_BYTES;
+                    const unsigned b_dst = a_dst + MC_TC2_A_BYTES;
+                    if (leader) mc_mbar_expect_tx(full_local, 2 * MC_TC2_STAGE_BYTES);
+                    mc_tma_load_2d_pair(a_dst, &map_a, full_leader, kb * kBlockK, row0);
+                    if (kBIsKMajor) {
+                        mc_tma_load_2d_pair(b_dst, &map_b, full_leader, kb * kBlockK, col0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 128 / kAtomN; ++j) {
+                            mc_tma_load_2d_pair(b_dst + j * (kBlockK * 128), &map_b, full_leader, col0 + j * kAtomN, kb * kBlockK);
+                        }
+                    }
+                    ++issued;
+                    if (++stage == MC_TC2_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok && leader) {
+                // Let the copies in flight land before shared memory is released (the leader's barriers see both CTAs').
+                int s = stage;
+                unsigned ph = phase;
+                const int pending = min(issued, MC_TC2_STAGES);
+                for (int i = 0; i < pending; ++i) {
+                    if (s == 0) {
+                        s = MC_TC2_STAGES;
+                        ph ^= 1u;
+                    }
+                    --s;
+                    const unsigned long long t0 = mc_globaltimer();
+                    while (!mc_mbar_try_wait(bar_full + 8 * s, ph)) {
+                        if (mc_globaltimer() - t0 > MC_TC_WAIT_NS / 4) {
+                            if (p.status != nullptr) atomicOr(p.status, MC_TC_ERR_DRAIN);
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            int stage = 0;
+            unsigned phase = 0;
+            int acc = 0;
+            unsigned acc_phase = 0;
+            bool ok = true;
+            for (int item = cluster_id; ok && item < items; item += num_clusters) {
+                ok = mc_mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, MC_TC_ERR_MMA);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned tmem_d = tmem_base + (unsigned)(acc * MC_TC_BN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    ok = mc_mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, MC_TC_ERR_MMA);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned a_src = tiles_base + stage * MC_TC2_STAGE_BYTES;
+                    const unsigned b_src = a_src + MC_TC2_A_BYTES;
+                    const unsigned long long desc_a = mc_smem_desc(a_src, 16, 1024);
+                    const unsigned long long desc_b =
+                        kBIsKMajor ? mc_smem_desc(b_src, 16, 1024) : mc_smem_desc(b_src, kBlockK * 128, 1024);
+                    const unsigned b_step = kBIsKMajor ? 2u : (unsigned)(kMmaK * 128) >> 4;
+#pragma unroll
+                    for (int ks = 0; ks < kMmasPerBlock; ++ks) {
+                        mc_umma_pair(tmem_d, desc_a + (unsigned long long)(2 * ks), desc_b + (unsigned long long)(b_step * ks),
+                                     p.idesc, (kb > 0 || ks > 0) ? 1u : 0u, kTf32);
+                    }
+                    mc_umma_commit_pair(bar_empty + 8 * stage);
+                    if (++stage == MC_TC2_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                mc_umma_commit_pair(bar_tmem_full + 8 * acc);
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------------------------ epilogue (both CTAs, own 128 rows each)
+        const int quarter = warp & 3;
+        constexpr int kColsPerWarp = MC_TC_BN / (MC_TC_EPILOGUE_WARPS / 4);
+        const int col_begin = ((warp - 2) >> 2) * kColsPerWarp;
+        int acc = 0;
+        unsigned acc_phase = 0;
+        bool ok = true;
+        for (int item = cluster_id; ok && item < items; item += num_clusters) {
+            int mp, nb;
+            decode(item, mp, nb);
+            ok = mc_mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, p.status, MC_TC_ERR_EPILOGUE);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = (2 * mp + (int)rank) * MC_TC_BM + quarter * 32 + lane;
+            const int n0 = nb * MC_TC_BN;
+            const bool vec4 = (p.ldc & 3) == 0 && (((unsigned long long)p.c) & 15) == 0;
+            const bool vec16 = (p.ldc16 & 7) == 0 && (((unsigned long long)p.c16) & 15) == 0;
+#pragma unroll 1
+            for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {
+                const int col_local = col_begin + chunk * 32;
+                const int col0 = n0 + col_local;
+                if (col0 >= p.n) break;
+                unsigned v[32];
+                mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * MC_TC_BN + col_local), v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < p.m) {
+                    float f[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                    if (col0 + 32 <= p.n) {
+                        mc_epilogue32(f, (unsigned)row, (unsigned)col0, epi);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (col0 + j < p.n) f[j] = mc_epilogue(f[j], (unsigned)row, (unsigned)(col0 + j), epi);
+                        }
+                    }
+                    if (p.c != nullptr) {
+                        float* out = p.c + (long long)row * p.ldc + col0;
+                        if (vec4 && col0 + 32 <= p.n) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                *reinterpret_cast<float4*>(out + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (col0 + j < p.n) out[j] = f[j];
+                            }
+                        }
+                    }
+                    if (p.c16 != nullptr) {
+                        unsigned short* out16 = p.c16 + (long long)row * p.ldc16 + col0;
+                        if (vec16 && col0 + 32 <= p.n) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 pack;
+                                pack.x = mc_to_half2(f[j + 0], f[j + 1], p.c16_kind);
+                                pack.y = mc_to_half2(f[j + 2], f[j + 3], p.c16_kind);
+                                pack.z = mc_to_half2(f[j + 4], f[j + 5], p.c16_kind);
+                                pack.w = mc_to_half2(f[j + 6], f[j + 7], p.c16_kind);
+                                *reinterpret_cast<uint4*>(out16 + j) = pack;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (col0 + j < p.n) out16[j] = mc_to_half(f[j], p.c16_kind);
+                            }
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mc_mbar_arrive_cluster(mc_mapa(bar_tmem_empty + 8 * acc, 0));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    __syncwarp();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    mc_cluster_sync();  // neither CTA lets go of its shared memory or TMEM while the peer may still touch them
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
+mc_gemm_tc2_h16_bmn(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
+                    const McEpilogueArgs epi) {
+    mc_gemm_tc2_body<2, false>(map_a, map_b, p, epi);
+}
+
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
+mc_gemm_tc2_h16_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
+                   const McEpilogueArgs epi) {
+    mc_gemm_tc2_body<2, true>(map_a, map_b, p, epi);
+}
+
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
+mc_gemm_tc2_tf32_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
+                    const McEpilogueArgs epi) {
+    mc_gemm_tc2_body<4, true>(map_a, map_b, p, epi);
+}

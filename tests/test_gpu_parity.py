@@ -211,7 +211,7 @@ def _torch():
     return torch
 
 
-def _device_gemm(mc, arith, a, b, splits, b_transposed=False, half=None):
+def _device_gemm(mc, arith, a, b, splits, b_transposed=False, half=None, variant=0):
     """Calls mcd_gemm directly with device buffers held by torch; C is pre-filled with NaN."""
     torch = _torch()
     lib = mc.lib()
@@ -258,6 +258,7 @@ def _device_gemm(mc, arith, a, b, splits, b_transposed=False, half=None):
     args.a, args.b, args.lda, args.ldb, args.b_transposed = ta.data_ptr(), tb.data_ptr(), lda, ldb, int(b_transposed)
     args.c, args.ldc, args.splits, args.workspace = tc.data_ptr(), n, splits, ws.data_ptr()
     args.status = status.data_ptr()
+    args.variant = variant
     lib.mcd_gemm.restype = C.c_int
     lib.mcd_last_error.restype = C.c_char_p
     stream = torch.cuda.current_stream().cuda_stream
@@ -298,6 +299,27 @@ def test_tensor_core_kernel_direct(mc, oracle, name, arith, half, u, sub, layout
         for splits in [1, 3]:
             got = _device_gemm(mc, arith, a, b, splits, b_transposed=layout, half=half)
             check_bound(got, exact, abs_dot, k, u, sub, f"{name} {m}x{k}x{n} splits={splits} transposed={layout}")
+
+
+@pytest.mark.parametrize("layout", [False, True])
+@pytest.mark.parametrize("name,arith,half,u,sub", TC_KINDS)
+def test_tensor_core_pair_kernel_direct(mc, oracle, name, arith, half, u, sub, layout):
+    """The SM-pair (cta_group::2) kernel, forced with variant bit 8, against the one-CTA kernel (bit 4): the two
+    accumulate every output in the same order, so they agree bit for bit; and against the float64 bound."""
+    if half is None and not layout:
+        pytest.skip("TF32 reads B as a [n,k] copy only")
+    for m, k, n in [(256, 64, 256), (256, 512, 512), (128, 256, 256), (300, 1004, 36), (33, 264, 72), (1024, 1024, 1024),
+                    (1300, 520, 2000), (5000, 256, 4200)]:
+        if half is None and (k % 4 or n % 4):
+            continue
+        a = oracle.uniform_values(m * k, 1, -1, 1).reshape(m, k)
+        b = oracle.uniform_values(k * n, 2, -1, 1).reshape(k, n)
+        pair = _device_gemm(mc, arith, a, b, 1, b_transposed=layout, half=half, variant=8)
+        single = _device_gemm(mc, arith, a, b, 1, b_transposed=layout, half=half, variant=4)
+        assert np.array_equal(pair, single), f"{name} {m}x{k}x{n} transposed={layout}: pair and one-CTA kernels differ"
+        if m * n <= 1 << 21:
+            exact, abs_dot = exact_and_abs(a, b)
+            check_bound(pair, exact, abs_dot, k, u, sub, f"{name} pair {m}x{k}x{n} transposed={layout}")
 
 
 @pytest.mark.parametrize("name,arith,half,u,sub", TC_KINDS)
