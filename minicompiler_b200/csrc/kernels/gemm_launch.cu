@@ -264,12 +264,13 @@ int tc_splits(const mcd_gemm_args* a) {
 
 // Whether the launch goes to the SM-pair kernel: unsplit problems whose 256 x 256 pair tiles give every SM pair
 // at least kPairMinWaves tiles; variant bit 8 forces it for any unsplit problem, bit 4 turns it off.
-constexpr int kPairMinWaves = 4;
+constexpr int kPairMinWaves = 1;
 bool tc_uses_pairs(const mcd_gemm_args* a) {
     if (a->arith == MCD_GEMM_F32 || tc_splits(a) != 1 || (a->variant & 4) != 0) return false;
     if (a->arith == MCD_GEMM_TF32 && a->b_transposed == 0) return false;
     if ((a->variant & 8) != 0) return true;
     const long long tiles_m = (a->m + MC_TC_BM - 1) / MC_TC_BM;
+    if (tiles_m % 2 != 0 && tiles_m < 9) return false;  // the odd row block's partner would idle
     const long long items = ((tiles_m + 1) / 2) * ((a->n + MC_TC_BN - 1) / MC_TC_BN);
     return items >= static_cast<long long>(kPairMinWaves) * (sm_count_of_current_device() / 2);
 }
@@ -324,6 +325,7 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     p.idesc = instruction_descriptor(a->arith, b_k_major);
     p.k_blocks_per_split = per;
     p.splits = splits;
+    p.tune = a->variant >> 8;
     // Tiles that do not fill the last wave of CTAs are cut in two when both halves of all of them fit in one wave.
     const int sms = sm_count_of_current_device();
     const int all_tiles = ((a->m + MC_TC_BM - 1) / MC_TC_BM) * ((a->n + MC_TC_BN - 1) / MC_TC_BN);
@@ -332,11 +334,14 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     McEpilogueArgs epi = epilogue_args(a);
 
     if (pairs) {
-        p.half_tiles = 0;
         p.idesc = (p.idesc & ~(0x1Fu << 24)) | (static_cast<unsigned>(2 * MC_TC_BM >> 4) << 24);  // M = 256 over the pair
         const int tiles_m = (a->m + MC_TC_BM - 1) / MC_TC_BM;
-        const int items = ((tiles_m + 1) / 2) * ((a->n + MC_TC_BN - 1) / MC_TC_BN);
-        const unsigned pair_grid = 2u * static_cast<unsigned>(std::max(1, std::min(items, sms / 2)));
+        const int pair_tiles = ((tiles_m + 1) / 2) * ((a->n + MC_TC_BN - 1) / MC_TC_BN);
+        const int clusters = sms / 2;
+        const int pair_tail = pair_tiles % clusters;
+        p.half_tiles = ((a->variant & 2) == 0 && pair_tail > 0 && 2 * pair_tail <= clusters) ? pair_tail : 0;
+        const int items = pair_tiles + p.half_tiles;
+        const unsigned pair_grid = 2u * static_cast<unsigned>(std::max(1, std::min(items, clusters)));
         if (a->function != nullptr) {
             void* params[] = {&map_a, &map_b, &p, &epi};
             return mcd_launch(a->function, pair_grid, 1, 1, MC_TC_THREADS, MC_TC2_SMEM_BYTES, s, params);

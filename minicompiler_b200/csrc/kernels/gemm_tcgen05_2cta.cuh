@@ -116,7 +116,7 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
     const int pairs_m = (tiles_m + 1) / 2;
     const int tiles_n = (p.n + MC_TC_BN - 1) / MC_TC_BN;
     const int k_blocks = (p.k + kBlockK - 1) / kBlockK;
-    const int items = pairs_m * tiles_n;
+    const int items = pairs_m * tiles_n + p.half_tiles;
 
     if (threadIdx.x == 0) {
         abort_flag_storage = 0;
@@ -142,13 +142,22 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = tmem_base_slot;
 
-    auto decode = [&](int item, int& mp, int& nb) {
+    // Work item -> (row pair, column block, column half). The last `half_tiles` tiles are issued as two 128-column
+    // halves each (half = 0 / 1, otherwise -1) so that a short last wave spreads over twice as many SM pairs.
+    const int whole = pairs_m * tiles_n - p.half_tiles;
+    auto decode = [&](int item, int& mp, int& nb, int& half) {
         constexpr int kBand = MC_TC_RASTER / 2;
+        half = -1;
+        int tile = item;
+        if (item >= whole) {
+            half = (item - whole) & 1;
+            tile = whole + ((item - whole) >> 1);
+        }
         const int band_tiles = kBand * tiles_n;
-        const int band = item / band_tiles;
+        const int band = tile / band_tiles;
         const int first = band * kBand;
         const int band_rows = min(kBand, pairs_m - first);
-        const int within = item - band * band_tiles;
+        const int within = tile - band * band_tiles;
         mp = first + within % band_rows;
         nb = within / band_rows;
     };
@@ -161,10 +170,12 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
             int issued = 0;
             bool ok = true;
             for (int item = cluster_id; ok && item < items; item += num_clusters) {
-                int mp, nb;
-                decode(item, mp, nb);
+                int mp, nb, half;
+                decode(item, mp, nb, half);
                 const int row0 = (2 * mp + (int)rank) * MC_TC_BM;
-                const int col0 = nb * MC_TC_BN + (int)rank * 128;
+                // A whole tile: this CTA's 128 of the 256 columns. A half tile: its 64 of the half's 128 columns,
+                // fetched with the same 128-column copies (the upper 64 are not used).
+                const int col0 = nb * MC_TC_BN + (half < 0 ? (int)rank * 128 : half * 128 + (int)rank * 64);
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     ok = mc_mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, MC_TC_ERR_PRODUCER);
                     if (!ok) break;
@@ -223,6 +234,8 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned tmem_d = tmem_base + (unsigned)(acc * MC_TC_BN);
+                // N field of the instruction descriptor (bits 17-22, N >> 3): 128 for a half tile.
+                const unsigned idesc = item < whole ? p.idesc : ((p.idesc & ~(0x3Fu << 17)) | ((unsigned)(MC_TC_BN / 2 >> 3) << 17));
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     ok = mc_mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, MC_TC_ERR_MMA);
                     if (!ok) break;
@@ -236,7 +249,7 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
 #pragma unroll
                     for (int ks = 0; ks < kMmasPerBlock; ++ks) {
                         mc_umma_pair(tmem_d, desc_a + (unsigned long long)(2 * ks), desc_b + (unsigned long long)(b_step * ks),
-                                     p.idesc, (kb > 0 || ks > 0) ? 1u : 0u, kTf32);
+                                     idesc, (kb > 0 || ks > 0) ? 1u : 0u, kTf32);
                     }
                     mc_umma_commit_pair(bar_empty + 8 * stage);
                     if (++stage == MC_TC2_STAGES) {
@@ -259,8 +272,8 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
         unsigned acc_phase = 0;
         bool ok = true;
         for (int item = cluster_id; ok && item < items; item += num_clusters) {
-            int mp, nb;
-            decode(item, mp, nb);
+            int mp, nb, half;
+            decode(item, mp, nb, half);
             ok = mc_mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, p.status, MC_TC_ERR_EPILOGUE);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -269,13 +282,17 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
             const int n0 = nb * MC_TC_BN;
             const bool vec4 = (p.ldc & 3) == 0 && (((unsigned long long)p.c) & 15) == 0;
             const bool vec16 = (p.ldc16 & 7) == 0 && (((unsigned long long)p.c16) & 15) == 0;
+            // A whole tile: this warp's half of 256 columns. A half tile: this warp's half of its 128 columns,
+            // which sit in accumulator columns 0..127.
+            const int warp_cols = half < 0 ? kColsPerWarp : kColsPerWarp / 2;
+            const int acc_col_begin = half < 0 ? col_begin : col_begin / 2;
+            const int tile_col_begin = half < 0 ? col_begin : half * (MC_TC_BN / 2) + col_begin / 2;
 #pragma unroll 1
-            for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {
-                const int col_local = col_begin + chunk * 32;
-                const int col0 = n0 + col_local;
-                if (col0 >= p.n) break;
+            for (int chunk = 0; chunk < warp_cols / 32; ++chunk) {
+                const int col0 = n0 + tile_col_begin + chunk * 32;
+                if (col0 >= p.n) break;  // warp-uniform
                 unsigned v[32];
-                mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * MC_TC_BN + col_local), v);
+                mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * MC_TC_BN + acc_col_begin + chunk * 32), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (row < p.m) {
                     float f[32];

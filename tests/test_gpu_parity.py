@@ -309,7 +309,7 @@ def test_tensor_core_pair_kernel_direct(mc, oracle, name, arith, half, u, sub, l
     if half is None and not layout:
         pytest.skip("TF32 reads B as a [n,k] copy only")
     for m, k, n in [(256, 64, 256), (256, 512, 512), (128, 256, 256), (300, 1004, 36), (33, 264, 72), (1024, 1024, 1024),
-                    (1300, 520, 2000), (5000, 256, 4200)]:
+                    (1300, 520, 2000), (5000, 256, 4200), (1024, 136, 2048), (4096, 256, 4096)]:
         if half is None and (k % 4 or n % 4):
             continue
         a = oracle.uniform_values(m * k, 1, -1, 1).reshape(m, k)
