@@ -275,6 +275,21 @@ bool tc_uses_pairs(const mcd_gemm_args* a) {
     return items >= static_cast<long long>(kPairMinWaves) * (sm_count_of_current_device() / 2);
 }
 
+// Whether the SM-pair kernel takes two 256-column tiles per work item.
+// That form saves a quarter of the operand traffic per flop but cannot overlap a tile's epilogue with the next
+// tile's MMAs, so it pays for long K only: from 128 K blocks (8192 elements of 16 bits) upwards, when the
+// problem holds at least two waves of such items. Variant bit 16 forces it, bit 32 turns it off.
+bool tc_pair_wide(const mcd_gemm_args* a) {
+    if ((a->variant & 32) != 0) return false;
+    if ((a->variant & 16) != 0) return true;
+    const int block_k = a->arith == MCD_GEMM_TF32 ? 32 : 64;
+    const long long k_blocks = (a->k + block_k - 1) / block_k;
+    const long long tiles_m = (a->m + MC_TC_BM - 1) / MC_TC_BM;
+    const long long tiles_n = (a->n + MC_TC_BN - 1) / MC_TC_BN;
+    const long long wide_tiles = ((tiles_m + 1) / 2) * ((tiles_n + 1) / 2);
+    return k_blocks >= 128 && wide_tiles >= 2LL * (sm_count_of_current_device() / 2);
+}
+
 int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     const bool tf32 = a->arith == MCD_GEMM_TF32;
     const int elem = tf32 ? 4 : 2;
@@ -325,7 +340,7 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     p.idesc = instruction_descriptor(a->arith, b_k_major);
     p.k_blocks_per_split = per;
     p.splits = splits;
-    p.tune = a->variant >> 8;
+    p.wide = 0;
     // Tiles that do not fill the last wave of CTAs are cut in two when both halves of all of them fit in one wave.
     const int sms = sm_count_of_current_device();
     const int all_tiles = ((a->m + MC_TC_BM - 1) / MC_TC_BM) * ((a->n + MC_TC_BN - 1) / MC_TC_BN);
@@ -336,7 +351,9 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     if (pairs) {
         p.idesc = (p.idesc & ~(0x1Fu << 24)) | (static_cast<unsigned>(2 * MC_TC_BM >> 4) << 24);  // M = 256 over the pair
         const int tiles_m = (a->m + MC_TC_BM - 1) / MC_TC_BM;
-        const int pair_tiles = ((tiles_m + 1) / 2) * ((a->n + MC_TC_BN - 1) / MC_TC_BN);
+        const int tiles_n = (a->n + MC_TC_BN - 1) / MC_TC_BN;
+        p.wide = (tc_pair_wide(a) ? 1 : 0) | ((a->variant >> 8) << 8);
+        const int pair_tiles = ((tiles_m + 1) / 2) * ((p.wide & 1) ? (tiles_n + 1) / 2 : tiles_n);
         const int clusters = sms / 2;
         const int pair_tail = pair_tiles % clusters;
         p.half_tiles = ((a->variant & 2) == 0 && pair_tail > 0 && 2 * pair_tail <= clusters) ? pair_tail : 0;

@@ -59,7 +59,7 @@ struct McTcParams {
     int k_blocks_per_split;  // K blocks (of 128 bytes) per work item
     int splits;
     int half_tiles;  // the last `half_tiles` tiles are each issued as two 128-column work items (splits == 1 only)
-    int tune;        // experiment switches (variant >> 8); 0 in normal use
+    int wide;        // SM-pair kernel only: two 256-column tiles per work item
 };
 
 __device__ __forceinline__ unsigned mc_smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }

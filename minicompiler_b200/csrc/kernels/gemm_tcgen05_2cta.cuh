@@ -18,6 +18,7 @@
 // This text follows gemm_tcgen05.cuh in the same translation unit and uses its helpers.
 
 #define MC_TC2_STAGES 6
+#define MC_TC2_WIDE_STAGES 4
 #define MC_TC2_A_BYTES (MC_TC_BM * 128)
 #define MC_TC2_B_BYTES (128 * 128)
 #define MC_TC2_STAGE_BYTES (MC_TC2_A_BYTES + MC_TC2_B_BYTES)
@@ -93,6 +94,14 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
     constexpr int kAtomN = 128 / kElemBytes;
     constexpr bool kTf32 = kElemBytes == 4;
 
+    // Two shapes of work item share this body. Normal: one 256 x 256 tile per item, the two TMEM regions used
+    // in turn so that the epilogue of one item overlaps the MMAs of the next; 32 KB stages, 6 deep. Wide
+    // (p.wide): two 256 x 256 tiles side by side per item, one per TMEM region, fed by the same A rows - a CTA
+    // then loads 48 KB per K block for twice the arithmetic; 48 KB stages, 4 deep.
+    const bool wide = (p.wide & 1) != 0;
+    const int stages = (p.wide >> 8) ? (p.wide >> 8) : wide ? MC_TC2_WIDE_STAGES : MC_TC2_STAGES;
+    const unsigned stage_bytes = wide ? (unsigned)(MC_TC2_A_BYTES + 2 * MC_TC2_B_BYTES) : (unsigned)MC_TC2_STAGE_BYTES;
+
     extern __shared__ unsigned char mc_tc_smem_raw[];
     const unsigned raw = mc_smem_addr(mc_tc_smem_raw);
     const unsigned tiles_base = (raw + 1023u) & ~1023u;
@@ -116,7 +125,11 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
     const int pairs_m = (tiles_m + 1) / 2;
     const int tiles_n = (p.n + MC_TC_BN - 1) / MC_TC_BN;
     const int k_blocks = (p.k + kBlockK - 1) / kBlockK;
-    const int items = pairs_m * tiles_n + p.half_tiles;
+    const int cols_n = wide ? (tiles_n + 1) / 2 : tiles_n;  // column tiles of this mode
+    // The last `half_tiles` tiles are issued as two items each, so that a short last wave spreads over twice as
+    // many SM pairs: a normal tile as its two 128-column halves, a wide tile as its two 256-column tiles.
+    const int whole = pairs_m * cols_n - p.half_tiles;
+    const int items = whole + 2 * p.half_tiles;
 
     if (threadIdx.x == 0) {
         abort_flag_storage = 0;
@@ -142,24 +155,32 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = tmem_base_slot;
 
-    // Work item -> (row pair, column block, column half). The last `half_tiles` tiles are issued as two 128-column
-    // halves each (half = 0 / 1, otherwise -1) so that a short last wave spreads over twice as many SM pairs.
-    const int whole = pairs_m * tiles_n - p.half_tiles;
-    auto decode = [&](int item, int& mp, int& nb, int& half) {
+    // Work item -> row pair `mp`, first 256-column block `nb`, number of 256-column tiles `nsub` (0: nothing to
+    // do), and `half` = 0 / 1 when the item is a 128-column half of a normal tile (-1 otherwise).
+    auto decode = [&](int item, int& mp, int& nb, int& nsub, int& half) {
         constexpr int kBand = MC_TC_RASTER / 2;
-        half = -1;
+        int part = -1;
         int tile = item;
         if (item >= whole) {
-            half = (item - whole) & 1;
+            part = (item - whole) & 1;
             tile = whole + ((item - whole) >> 1);
         }
-        const int band_tiles = kBand * tiles_n;
+        const int band_tiles = kBand * cols_n;
         const int band = tile / band_tiles;
         const int first = band * kBand;
         const int band_rows = min(kBand, pairs_m - first);
         const int within = tile - band * band_tiles;
         mp = first + within % band_rows;
-        nb = within / band_rows;
+        const int col = within / band_rows;
+        half = -1;
+        if (wide) {
+            nb = part < 0 ? 2 * col : 2 * col + part;
+            nsub = part < 0 ? min(2, tiles_n - nb) : (nb < tiles_n ? 1 : 0);
+        } else {
+            nb = col;
+            nsub = 1;
+            half = part;
+        }
     };
 
     if (warp == 0) {
@@ -170,31 +191,36 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
             int issued = 0;
             bool ok = true;
             for (int item = cluster_id; ok && item < items; item += num_clusters) {
-                int mp, nb, half;
-                decode(item, mp, nb, half);
+                int mp, nb, nsub, half;
+                decode(item, mp, nb, nsub, half);
+                if (nsub == 0) continue;
                 const int row0 = (2 * mp + (int)rank) * MC_TC_BM;
                 // A whole tile: this CTA's 128 of the 256 columns. A half tile: its 64 of the half's 128 columns,
                 // fetched with the same 128-column copies (the upper 64 are not used).
-                const int col0 = nb * MC_TC_BN + (half < 0 ? (int)rank * 128 : half * 128 + (int)rank * 64);
+                const int col_first = nb * MC_TC_BN + (half < 0 ? (int)rank * 128 : half * 128 + (int)rank * 64);
+                const unsigned bytes = (unsigned)(MC_TC2_A_BYTES + nsub * MC_TC2_B_BYTES);
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     ok = mc_mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, MC_TC_ERR_PRODUCER);
                     if (!ok) break;
                     const unsigned full_local = bar_full + 8 * stage;
                     const unsigned full_leader = mc_mapa(full_local, 0);
-                    const unsigned a_dst = tiles_base + stage * MC_TC2_STAGE_BYTES;
-                    const unsigned b_dst = a_dst + MC_TC2_A_BYTES;
-                    if (leader) mc_mbar_expect_tx(full_local, 2 * MC_TC2_STAGE_BYTES);
+                    const unsigned a_dst = tiles_base + stage * stage_bytes;
+                    if (leader) mc_mbar_expect_tx(full_local, 2 * bytes);
                     mc_tma_load_2d_pair(a_dst, &map_a, full_leader, kb * kBlockK, row0);
-                    if (kBIsKMajor) {
-                        mc_tma_load_2d_pair(b_dst, &map_b, full_leader, kb * kBlockK, col0);
-                    } else {
+                    for (int s = 0; s < nsub; ++s) {
+                        const unsigned b_dst = a_dst + MC_TC2_A_BYTES + s * MC_TC2_B_BYTES;
+                        const int col0 = col_first + s * MC_TC_BN;
+                        if (kBIsKMajor) {
+                            mc_tma_load_2d_pair(b_dst, &map_b, full_leader, kb * kBlockK, col0);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < 128 / kAtomN; ++j) {
-                            mc_tma_load_2d_pair(b_dst + j * (kBlockK * 128), &map_b, full_leader, col0 + j * kAtomN, kb * kBlockK);
+                            for (int j = 0; j < 128 / kAtomN; ++j) {
+                                mc_tma_load_2d_pair(b_dst + j * (kBlockK * 128), &map_b, full_leader, col0 + j * kAtomN, kb * kBlockK);
+                            }
                         }
                     }
                     ++issued;
-                    if (++stage == MC_TC2_STAGES) {
+                    if (++stage == stages) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -204,10 +230,10 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                 // Let the copies in flight land before shared memory is released (the leader's barriers see both CTAs').
                 int s = stage;
                 unsigned ph = phase;
-                const int pending = min(issued, MC_TC2_STAGES);
+                const int pending = min(issued, stages);
                 for (int i = 0; i < pending; ++i) {
                     if (s == 0) {
-                        s = MC_TC2_STAGES;
+                        s = stages;
                         ph ^= 1u;
                     }
                     --s;
@@ -226,41 +252,82 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
         if (lane == 0 && leader) {
             int stage = 0;
             unsigned phase = 0;
-            int acc = 0;
-            unsigned acc_phase = 0;
+            int acc = 0;              // normal mode: the TMEM region of this item
+            unsigned empty_phase = 0;  // bit r: parity of region r's tmem_empty barrier
             bool ok = true;
             for (int item = cluster_id; ok && item < items; item += num_clusters) {
-                ok = mc_mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, MC_TC_ERR_MMA);
+                int mp, nb, nsub, half;
+                decode(item, mp, nb, nsub, half);
+                if (nsub == 0) continue;
+                const int region0 = wide ? 0 : acc;
+                ok = mc_mbar_wait(bar_tmem_empty + 8 * region0, ((empty_phase >> region0) & 1u) ^ 1u, abort_flag, p.status,
+                                  MC_TC_ERR_MMA);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned tmem_d = tmem_base + (unsigned)(acc * MC_TC_BN);
                 // N field of the instruction descriptor (bits 17-22, N >> 3): 128 for a half tile.
-                const unsigned idesc = item < whole ? p.idesc : ((p.idesc & ~(0x3Fu << 17)) | ((unsigned)(MC_TC_BN / 2 >> 3) << 17));
-                for (int kb = 0; kb < k_blocks; ++kb) {
-                    ok = mc_mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, MC_TC_ERR_MMA);
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const unsigned a_src = tiles_base + stage * MC_TC2_STAGE_BYTES;
-                    const unsigned b_src = a_src + MC_TC2_A_BYTES;
+                const unsigned idesc = half < 0 ? p.idesc : ((p.idesc & ~(0x3Fu << 17)) | ((unsigned)(MC_TC_BN / 2 >> 3) << 17));
+                const unsigned b_step = kBIsKMajor ? 2u : (unsigned)(kMmaK * 128) >> 4;
+                auto issue = [&](int st, int s, bool first_block) {
+                    const unsigned a_src = tiles_base + st * stage_bytes;
+                    const unsigned b_src = a_src + MC_TC2_A_BYTES + s * MC_TC2_B_BYTES;
+                    const unsigned tmem_d = tmem_base + (unsigned)((region0 + s) * MC_TC_BN);
                     const unsigned long long desc_a = mc_smem_desc(a_src, 16, 1024);
                     const unsigned long long desc_b =
                         kBIsKMajor ? mc_smem_desc(b_src, 16, 1024) : mc_smem_desc(b_src, kBlockK * 128, 1024);
-                    const unsigned b_step = kBIsKMajor ? 2u : (unsigned)(kMmaK * 128) >> 4;
 #pragma unroll
                     for (int ks = 0; ks < kMmasPerBlock; ++ks) {
-                        mc_umma_pair(tmem_d, desc_a + (unsigned long long)(2 * ks), desc_b + (unsigned long long)(b_step * ks),
-                                     idesc, (kb > 0 || ks > 0) ? 1u : 0u, kTf32);
+                        mc_umma_pair(tmem_d, desc_a + (unsigned long long)(2 * ks), desc_b + (unsigned long long)(b_step * ks), idesc,
+                                     (!first_block || ks > 0) ? 1u : 0u, kTf32);
                     }
+                };
+                int kb = 0;
+                if (nsub == 2) {
+                    // The second region may still be draining: start on the first with as many K blocks as the ring
+                    // holds, then catch the second region up on the same blocks and release them.
+                    const int head = min(stages, k_blocks);
+                    int st = stage;
+                    unsigned ph = phase;
+                    for (int i = 0; i < head; ++i) {
+                        ok = mc_mbar_wait(bar_full + 8 * st, ph, abort_flag, p.status, MC_TC_ERR_MMA);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        issue(st, 0, i == 0);
+                        if (++st == stages) {
+                            st = 0;
+                            ph ^= 1u;
+                        }
+                    }
+                    if (!ok) break;
+                    ok = mc_mbar_wait(bar_tmem_empty + 8 * 1, ((empty_phase >> 1) & 1u) ^ 1u, abort_flag, p.status, MC_TC_ERR_MMA);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    for (int i = 0; i < head; ++i) {
+                        issue(stage, 1, i == 0);
+                        mc_umma_commit_pair(bar_empty + 8 * stage);
+                        if (++stage == stages) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                    kb = head;
+                }
+                for (; kb < k_blocks; ++kb) {
+                    ok = mc_mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, MC_TC_ERR_MMA);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    for (int s = 0; s < nsub; ++s) issue(stage, s, kb == 0);
                     mc_umma_commit_pair(bar_empty + 8 * stage);
-                    if (++stage == MC_TC2_STAGES) {
+                    if (++stage == stages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                mc_umma_commit_pair(bar_tmem_full + 8 * acc);
+                for (int s = 0; s < nsub; ++s) {
+                    mc_umma_commit_pair(bar_tmem_full + 8 * (region0 + s));
+                    empty_phase ^= 1u << (region0 + s);
+                }
                 acc ^= 1;
-                if (acc == 0) acc_phase ^= 1u;
             }
         }
     } else {
@@ -268,84 +335,89 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
         const int quarter = warp & 3;
         constexpr int kColsPerWarp = MC_TC_BN / (MC_TC_EPILOGUE_WARPS / 4);
         const int col_begin = ((warp - 2) >> 2) * kColsPerWarp;
+        const bool vec4 = (p.ldc & 3) == 0 && (((unsigned long long)p.c) & 15) == 0;
+        const bool vec16 = (p.ldc16 & 7) == 0 && (((unsigned long long)p.c16) & 15) == 0;
         int acc = 0;
-        unsigned acc_phase = 0;
+        unsigned full_phase = 0;  // bit r: parity of region r's tmem_full barrier
         bool ok = true;
         for (int item = cluster_id; ok && item < items; item += num_clusters) {
-            int mp, nb, half;
-            decode(item, mp, nb, half);
-            ok = mc_mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, p.status, MC_TC_ERR_EPILOGUE);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            int mp, nb, nsub, half;
+            decode(item, mp, nb, nsub, half);
+            if (nsub == 0) continue;
+            const int region0 = wide ? 0 : acc;
             const int row = (2 * mp + (int)rank) * MC_TC_BM + quarter * 32 + lane;
-            const int n0 = nb * MC_TC_BN;
-            const bool vec4 = (p.ldc & 3) == 0 && (((unsigned long long)p.c) & 15) == 0;
-            const bool vec16 = (p.ldc16 & 7) == 0 && (((unsigned long long)p.c16) & 15) == 0;
             // A whole tile: this warp's half of 256 columns. A half tile: this warp's half of its 128 columns,
             // which sit in accumulator columns 0..127.
             const int warp_cols = half < 0 ? kColsPerWarp : kColsPerWarp / 2;
             const int acc_col_begin = half < 0 ? col_begin : col_begin / 2;
             const int tile_col_begin = half < 0 ? col_begin : half * (MC_TC_BN / 2) + col_begin / 2;
+            for (int s = 0; s < nsub; ++s) {
+                const int r = region0 + s;
+                ok = mc_mbar_wait(bar_tmem_full + 8 * r, (full_phase >> r) & 1u, abort_flag, p.status, MC_TC_ERR_EPILOGUE);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int n0 = (nb + s) * MC_TC_BN;
 #pragma unroll 1
-            for (int chunk = 0; chunk < warp_cols / 32; ++chunk) {
-                const int col0 = n0 + tile_col_begin + chunk * 32;
-                if (col0 >= p.n) break;  // warp-uniform
-                unsigned v[32];
-                mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * MC_TC_BN + acc_col_begin + chunk * 32), v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < p.m) {
-                    float f[32];
+                for (int chunk = 0; chunk < warp_cols / 32; ++chunk) {
+                    const int col0 = n0 + tile_col_begin + chunk * 32;
+                    if (col0 >= p.n) break;  // warp-uniform
+                    unsigned v[32];
+                    mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(r * MC_TC_BN + acc_col_begin + chunk * 32), v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (row < p.m) {
+                        float f[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                    if (col0 + 32 <= p.n) {
-                        mc_epilogue32(f, (unsigned)row, (unsigned)col0, epi);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (col0 + j < p.n) f[j] = mc_epilogue(f[j], (unsigned)row, (unsigned)(col0 + j), epi);
-                        }
-                    }
-                    if (p.c != nullptr) {
-                        float* out = p.c + (long long)row * p.ldc + col0;
-                        if (vec4 && col0 + 32 <= p.n) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                *reinterpret_cast<float4*>(out + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-                            }
+                        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                        if (col0 + 32 <= p.n) {
+                            mc_epilogue32(f, (unsigned)row, (unsigned)col0, epi);
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
-                                if (col0 + j < p.n) out[j] = f[j];
+                                if (col0 + j < p.n) f[j] = mc_epilogue(f[j], (unsigned)row, (unsigned)(col0 + j), epi);
                             }
                         }
-                    }
-                    if (p.c16 != nullptr) {
-                        unsigned short* out16 = p.c16 + (long long)row * p.ldc16 + col0;
-                        if (vec16 && col0 + 32 <= p.n) {
+                        if (p.c != nullptr) {
+                            float* out = p.c + (long long)row * p.ldc + col0;
+                            if (vec4 && col0 + 32 <= p.n) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint4 pack;
-                                pack.x = mc_to_half2(f[j + 0], f[j + 1], p.c16_kind);
-                                pack.y = mc_to_half2(f[j + 2], f[j + 3], p.c16_kind);
-                                pack.z = mc_to_half2(f[j + 4], f[j + 5], p.c16_kind);
-                                pack.w = mc_to_half2(f[j + 6], f[j + 7], p.c16_kind);
-                                *reinterpret_cast<uint4*>(out16 + j) = pack;
+                                for (int j = 0; j < 32; j += 4) {
+                                    *reinterpret_cast<float4*>(out + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    if (col0 + j < p.n) out[j] = f[j];
+                                }
                             }
-                        } else {
+                        }
+                        if (p.c16 != nullptr) {
+                            unsigned short* out16 = p.c16 + (long long)row * p.ldc16 + col0;
+                            if (vec16 && col0 + 32 <= p.n) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                if (col0 + j < p.n) out16[j] = mc_to_half(f[j], p.c16_kind);
+                                for (int j = 0; j < 32; j += 8) {
+                                    uint4 pack;
+                                    pack.x = mc_to_half2(f[j + 0], f[j + 1], p.c16_kind);
+                                    pack.y = mc_to_half2(f[j + 2], f[j + 3], p.c16_kind);
+                                    pack.z = mc_to_half2(f[j + 4], f[j + 5], p.c16_kind);
+                                    pack.w = mc_to_half2(f[j + 6], f[j + 7], p.c16_kind);
+                                    *reinterpret_cast<uint4*>(out16 + j) = pack;
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    if (col0 + j < p.n) out16[j] = mc_to_half(f[j], p.c16_kind);
+                                }
                             }
                         }
                     }
                 }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mc_mbar_arrive_cluster(mc_mapa(bar_tmem_empty + 8 * r, 0));
+                full_phase ^= 1u << r;
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mc_mbar_arrive_cluster(mc_mapa(bar_tmem_empty + 8 * acc, 0));
             acc ^= 1;
-            if (acc == 0) acc_phase ^= 1u;
         }
     }
 

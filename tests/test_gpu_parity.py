@@ -304,8 +304,9 @@ def test_tensor_core_kernel_direct(mc, oracle, name, arith, half, u, sub, layout
 @pytest.mark.parametrize("layout", [False, True])
 @pytest.mark.parametrize("name,arith,half,u,sub", TC_KINDS)
 def test_tensor_core_pair_kernel_direct(mc, oracle, name, arith, half, u, sub, layout):
-    """The SM-pair (cta_group::2) kernel, forced with variant bit 8, against the one-CTA kernel (bit 4): the two
-    accumulate every output in the same order, so they agree bit for bit; and against the float64 bound."""
+    """The SM-pair (cta_group::2) kernel, forced with variant bit 8 (bit 16: two tiles per work item), against the
+    one-CTA kernel (bit 4): they accumulate every output in the same order, so they agree bit for bit; and against
+    the float64 bound."""
     if half is None and not layout:
         pytest.skip("TF32 reads B as a [n,k] copy only")
     for m, k, n in [(256, 64, 256), (256, 512, 512), (128, 256, 256), (300, 1004, 36), (33, 264, 72), (1024, 1024, 1024),
@@ -315,8 +316,10 @@ def test_tensor_core_pair_kernel_direct(mc, oracle, name, arith, half, u, sub, l
         a = oracle.uniform_values(m * k, 1, -1, 1).reshape(m, k)
         b = oracle.uniform_values(k * n, 2, -1, 1).reshape(k, n)
         pair = _device_gemm(mc, arith, a, b, 1, b_transposed=layout, half=half, variant=8)
+        wide = _device_gemm(mc, arith, a, b, 1, b_transposed=layout, half=half, variant=8 | 16)
         single = _device_gemm(mc, arith, a, b, 1, b_transposed=layout, half=half, variant=4)
         assert np.array_equal(pair, single), f"{name} {m}x{k}x{n} transposed={layout}: pair and one-CTA kernels differ"
+        assert np.array_equal(wide, single), f"{name} {m}x{k}x{n} transposed={layout}: wide pair and one-CTA kernels differ"
         if m * n <= 1 << 21:
             exact, abs_dot = exact_and_abs(a, b)
             check_bound(pair, exact, abs_dot, k, u, sub, f"{name} pair {m}x{k}x{n} transposed={layout}")
