@@ -631,8 +631,11 @@ private:
                                  "' failed: " + mcd_last_error()};
                 }
             } else {
-                const std::string source = epilogue + mcd_gemm_source(g.arith);
-                if (mcd_jit_kernel(options_.device, source.c_str(), mcd_gemm_entry_point(&g), "--fmad=false", &g.function,
+                // Only the entry point this launch uses is compiled out of the kernel family's text.
+                const std::string entry = mcd_gemm_entry_point(&g);
+                const std::string source =
+                    "#define MC_SINGLE_ENTRY 1\n#define MC_ONLY_" + entry + " 1\n" + epilogue + mcd_gemm_source(g.arith);
+                if (mcd_jit_kernel(options_.device, source.c_str(), entry.c_str(), "--fmad=false", &g.function,
                                    &ms) != 0) {
                     return Error{std::string("compiling the epilogue of '") + graph_.node(step.result).name +
                                  "' failed: " + mcd_last_error()};

@@ -352,8 +352,8 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
         p.idesc = (p.idesc & ~(0x1Fu << 24)) | (static_cast<unsigned>(2 * MC_TC_BM >> 4) << 24);  // M = 256 over the pair
         const int tiles_m = (a->m + MC_TC_BM - 1) / MC_TC_BM;
         const int tiles_n = (a->n + MC_TC_BN - 1) / MC_TC_BN;
-        p.wide = (tc_pair_wide(a) ? 1 : 0) | ((a->variant >> 8) << 8);
-        const int pair_tiles = ((tiles_m + 1) / 2) * ((p.wide & 1) ? (tiles_n + 1) / 2 : tiles_n);
+        p.wide = tc_pair_wide(a) ? 1 : 0;
+        const int pair_tiles = ((tiles_m + 1) / 2) * (p.wide ? (tiles_n + 1) / 2 : tiles_n);
         const int clusters = sms / 2;
         const int pair_tail = pair_tiles % clusters;
         p.half_tiles = ((a->variant & 2) == 0 && pair_tail > 0 && 2 * pair_tail <= clusters) ? pair_tail : 0;
@@ -364,10 +364,12 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
             return mcd_launch(a->function, pair_grid, 1, 1, MC_TC_THREADS, MC_TC2_SMEM_BYTES, s, params);
         }
         using PairKernel = void (*)(const McTensorMap, const McTensorMap, const McTcParams, const McEpilogueArgs);
-        PairKernel kernel = tf32 ? mc_gemm_tc2_tf32_bk : (b_k_major ? mc_gemm_tc2_h16_bk : mc_gemm_tc2_h16_bmn);
+        PairKernel kernel = p.wide ? (tf32 ? mc_gemm_tc2w_tf32_bk : (b_k_major ? mc_gemm_tc2w_h16_bk : mc_gemm_tc2w_h16_bmn))
+                                   : (tf32 ? mc_gemm_tc2_tf32_bk : (b_k_major ? mc_gemm_tc2_h16_bk : mc_gemm_tc2_h16_bmn));
         static std::atomic<int> pair_configured{0};
         if (pair_configured.load() == 0) {
-            for (PairKernel kfn : {mc_gemm_tc2_tf32_bk, mc_gemm_tc2_h16_bk, mc_gemm_tc2_h16_bmn}) {
+            for (PairKernel kfn : {mc_gemm_tc2_tf32_bk, mc_gemm_tc2_h16_bk, mc_gemm_tc2_h16_bmn, mc_gemm_tc2w_tf32_bk,
+                                   mc_gemm_tc2w_h16_bk, mc_gemm_tc2w_h16_bmn}) {
                 if (int rc = check_rt(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_TC2_SMEM_BYTES),
                                       "cudaFuncSetAttribute(max dynamic shared memory)")) {
                     return rc;
@@ -456,6 +458,10 @@ extern "C" const char* mcd_gemm_entry_point(const mcd_gemm_args* a) {
         return vec ? "mc_gemm_f32_vec" : "mc_gemm_f32_any";
     }
     if (tc_uses_pairs(a)) {
+        if (tc_pair_wide(a)) {
+            if (a->arith == MCD_GEMM_TF32) return "mc_gemm_tc2w_tf32_bk";
+            return a->b_transposed ? "mc_gemm_tc2w_h16_bk" : "mc_gemm_tc2w_h16_bmn";
+        }
         if (a->arith == MCD_GEMM_TF32) return "mc_gemm_tc2_tf32_bk";
         return a->b_transposed ? "mc_gemm_tc2_h16_bk" : "mc_gemm_tc2_h16_bmn";
     }

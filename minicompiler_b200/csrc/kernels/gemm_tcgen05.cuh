@@ -458,26 +458,34 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
     }
 }
 
+#if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc_h16_bmn)
 extern "C" __global__ void __launch_bounds__(MC_TC_THREADS, 1)
 mc_gemm_tc_h16_bmn(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
                    const McTcParams p, const McEpilogueArgs epi) {
     mc_gemm_tc_body<2, false>(map_a, map_b, p, epi);
 }
+#endif
 
+#if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc_h16_bk)
 extern "C" __global__ void __launch_bounds__(MC_TC_THREADS, 1)
 mc_gemm_tc_h16_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
                   const McTcParams p, const McEpilogueArgs epi) {
     mc_gemm_tc_body<2, true>(map_a, map_b, p, epi);
 }
+#endif
 
+#if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc_tf32_bmn)
 extern "C" __global__ void __launch_bounds__(MC_TC_THREADS, 1)
 mc_gemm_tc_tf32_bmn(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
                     const McTcParams p, const McEpilogueArgs epi) {
     mc_gemm_tc_body<4, false>(map_a, map_b, p, epi);
 }
+#endif
 
+#if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc_tf32_bk)
 extern "C" __global__ void __launch_bounds__(MC_TC_THREADS, 1)
 mc_gemm_tc_tf32_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
                    const McTcParams p, const McEpilogueArgs epi) {
     mc_gemm_tc_body<4, true>(map_a, map_b, p, epi);
 }
+#endif

@@ -85,7 +85,7 @@ __device__ __forceinline__ void mc_umma_commit_pair(unsigned bar) {
                  : "memory");
 }
 
-template <int kElemBytes, bool kBIsKMajor>
+template <int kElemBytes, bool kBIsKMajor, bool kWide>
 __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const McTensorMap& map_b, const McTcParams& p,
                                                  const McEpilogueArgs& epi) {
     constexpr int kBlockK = 128 / kElemBytes;
@@ -98,9 +98,10 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
     // in turn so that the epilogue of one item overlaps the MMAs of the next; 32 KB stages, 6 deep. Wide
     // (p.wide): two 256 x 256 tiles side by side per item, one per TMEM region, fed by the same A rows - a CTA
     // then loads 48 KB per K block for twice the arithmetic; 48 KB stages, 4 deep.
-    const bool wide = (p.wide & 1) != 0;
-    const int stages = (p.wide >> 8) ? (p.wide >> 8) : wide ? MC_TC2_WIDE_STAGES : MC_TC2_STAGES;
-    const unsigned stage_bytes = wide ? (unsigned)(MC_TC2_A_BYTES + 2 * MC_TC2_B_BYTES) : (unsigned)MC_TC2_STAGE_BYTES;
+    constexpr bool wide = kWide;
+    constexpr int stages = kWide ? MC_TC2_WIDE_STAGES : MC_TC2_STAGES;
+    constexpr unsigned stage_bytes = kWide ? (unsigned)(MC_TC2_A_BYTES + 2 * MC_TC2_B_BYTES) : (unsigned)MC_TC2_STAGE_BYTES;
+    constexpr int kMaxSub = kWide ? 2 : 1;
 
     extern __shared__ unsigned char mc_tc_smem_raw[];
     const unsigned raw = mc_smem_addr(mc_tc_smem_raw);
@@ -207,7 +208,9 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                     const unsigned a_dst = tiles_base + stage * stage_bytes;
                     if (leader) mc_mbar_expect_tx(full_local, 2 * bytes);
                     mc_tma_load_2d_pair(a_dst, &map_a, full_leader, kb * kBlockK, row0);
-                    for (int s = 0; s < nsub; ++s) {
+#pragma unroll
+                    for (int s = 0; s < kMaxSub; ++s) {
+                        if (s >= nsub) break;
                         const unsigned b_dst = a_dst + MC_TC2_A_BYTES + s * MC_TC2_B_BYTES;
                         const int col0 = col_first + s * MC_TC_BN;
                         if (kBIsKMajor) {
@@ -281,7 +284,7 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                     }
                 };
                 int kb = 0;
-                if (nsub == 2) {
+                if (kWide && nsub == 2) {
                     // The second region may still be draining: start on the first with as many K blocks as the ring
                     // holds, then catch the second region up on the same blocks and release them.
                     const int head = min(stages, k_blocks);
@@ -315,7 +318,10 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                     ok = mc_mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, MC_TC_ERR_MMA);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    for (int s = 0; s < nsub; ++s) issue(stage, s, kb == 0);
+#pragma unroll
+                    for (int s = 0; s < kMaxSub; ++s) {
+                        if (s < nsub) issue(stage, s, kb == 0);
+                    }
                     mc_umma_commit_pair(bar_empty + 8 * stage);
                     if (++stage == stages) {
                         stage = 0;
@@ -358,17 +364,27 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int n0 = (nb + s) * MC_TC_BN;
-#pragma unroll 1
-                for (int chunk = 0; chunk < warp_cols / 32; ++chunk) {
+                // The warp's whole slice of the region goes to registers at once and the region is handed back to
+                // the MMA issuer before any arithmetic or store, so those overlap the next tile's MMAs.
+                unsigned v[kColsPerWarp / 32][32];
+#pragma unroll
+                for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {
+                    if (chunk * 32 < warp_cols) {
+                        mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(r * MC_TC_BN + acc_col_begin + chunk * 32),
+                                       v[chunk]);
+                    }
+                }
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mc_mbar_arrive_cluster(mc_mapa(bar_tmem_empty + 8 * r, 0));
+#pragma unroll
+                for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {
                     const int col0 = n0 + tile_col_begin + chunk * 32;
-                    if (col0 >= p.n) break;  // warp-uniform
-                    unsigned v[32];
-                    mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(r * MC_TC_BN + acc_col_begin + chunk * 32), v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (row < p.m) {
+                    if (chunk * 32 < warp_cols && col0 < p.n && row < p.m) {
                         float f[32];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[chunk][j]);
                         if (col0 + 32 <= p.n) {
                             mc_epilogue32(f, (unsigned)row, (unsigned)col0, epi);
                         } else {
@@ -412,9 +428,6 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                         }
                     }
                 }
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mc_mbar_arrive_cluster(mc_mapa(bar_tmem_empty + 8 * r, 0));
                 full_phase ^= 1u << r;
             }
             acc ^= 1;
@@ -431,20 +444,50 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
     }
 }
 
+#if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc2_h16_bmn)
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
 mc_gemm_tc2_h16_bmn(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
                     const McEpilogueArgs epi) {
-    mc_gemm_tc2_body<2, false>(map_a, map_b, p, epi);
+    mc_gemm_tc2_body<2, false, false>(map_a, map_b, p, epi);
 }
+#endif
 
+#if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc2_h16_bk)
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
 mc_gemm_tc2_h16_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
                    const McEpilogueArgs epi) {
-    mc_gemm_tc2_body<2, true>(map_a, map_b, p, epi);
+    mc_gemm_tc2_body<2, true, false>(map_a, map_b, p, epi);
 }
+#endif
 
+#if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc2_tf32_bk)
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
 mc_gemm_tc2_tf32_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
                     const McEpilogueArgs epi) {
-    mc_gemm_tc2_body<4, true>(map_a, map_b, p, epi);
+    mc_gemm_tc2_body<4, true, false>(map_a, map_b, p, epi);
 }
+#endif
+
+#if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc2w_h16_bmn)
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
+mc_gemm_tc2w_h16_bmn(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
+                     const McEpilogueArgs epi) {
+    mc_gemm_tc2_body<2, false, true>(map_a, map_b, p, epi);
+}
+#endif
+
+#if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc2w_h16_bk)
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
+mc_gemm_tc2w_h16_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
+                    const McEpilogueArgs epi) {
+    mc_gemm_tc2_body<2, true, true>(map_a, map_b, p, epi);
+}
+#endif
+
+#if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc2w_tf32_bk)
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
+mc_gemm_tc2w_tf32_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
+                     const McEpilogueArgs epi) {
+    mc_gemm_tc2_body<4, true, true>(map_a, map_b, p, epi);
+}
+#endif
