@@ -341,8 +341,9 @@ def main():
                    "h2d_bytes_per_step": int(sum(a.numel() * 4 for a in pinned_in)),
                    "d2h_bytes_per_step": int(sum(a.numel() * 4 for a in pinned_out)), "steps": e2e_steps,
                    "timing": "host wall clock around mc_run (it synchronizes), max over ranks",
-                   "path": "mc_run on pinned host buffers; a graph that only streams (every input read once, by generated "
-                           "elementwise kernels) reads and writes them in place over PCIe, any other graph is copied in and out"}
+                   "path": "mc_run on pinned host buffers; a graph that is one streaming elementwise launch is cut into slices "
+                           "whose H2D copy, kernel and D2H copy overlap on three streams, any other graph is copied in, run and "
+                           "copied out"}
 
         peaks = measured_peaks()
         median_ms = per_step[len(per_step) // 2]
