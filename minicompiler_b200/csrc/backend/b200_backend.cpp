@@ -613,6 +613,7 @@ private:
             uses_status_ = true;
         }
         if (step.has_epilogue) {
+            g.has_epilogue = 1;
             int slot = 0;
             for (std::size_t k = 0; k < step.inputs.size(); ++k) {
                 if (step.load_is_accumulator[k]) continue;

@@ -276,9 +276,10 @@ bool tc_uses_pairs(const mcd_gemm_args* a) {
 }
 
 // Whether the SM-pair kernel takes two 256-column tiles per work item.
-// That form saves a quarter of the operand traffic per flop but cannot overlap a tile's epilogue with the next
-// tile's MMAs, so it pays for long K only: from 128 K blocks (8192 elements of 16 bits) upwards, when the
-// problem holds at least two waves of such items. Variant bit 16 forces it, bit 32 turns it off.
+// That form saves a quarter of the operand traffic per flop, but the epilogue of an item's second tile is not
+// overlapped with MMAs as well as in the one-tile form. Measured: without a fused epilogue it wins from 32 K blocks
+// and one wave of items upwards; with one, only from 128 K blocks and two waves. Variant bit 16 forces it, bit 32
+// turns it off.
 bool tc_pair_wide(const mcd_gemm_args* a) {
     if ((a->variant & 32) != 0) return false;
     if ((a->variant & 16) != 0) return true;
@@ -287,7 +288,9 @@ bool tc_pair_wide(const mcd_gemm_args* a) {
     const long long tiles_m = (a->m + MC_TC_BM - 1) / MC_TC_BM;
     const long long tiles_n = (a->n + MC_TC_BN - 1) / MC_TC_BN;
     const long long wide_tiles = ((tiles_m + 1) / 2) * ((tiles_n + 1) / 2);
-    return k_blocks >= 128 && wide_tiles >= 2LL * (sm_count_of_current_device() / 2);
+    const long long clusters = sm_count_of_current_device() / 2;
+    const bool fused = a->has_epilogue != 0;
+    return fused ? (k_blocks >= 128 && wide_tiles >= 2 * clusters) : (k_blocks >= 32 && wide_tiles >= clusters);
 }
 
 int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
@@ -341,6 +344,7 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     p.k_blocks_per_split = per;
     p.splits = splits;
     p.wide = 0;
+    p.staged = (a->variant & 128) == 0 ? 1 : 0;
     // Tiles that do not fill the last wave of CTAs are cut in two when both halves of all of them fit in one wave.
     const int sms = sm_count_of_current_device();
     const int all_tiles = ((a->m + MC_TC_BM - 1) / MC_TC_BM) * ((a->n + MC_TC_BN - 1) / MC_TC_BN);
@@ -470,8 +474,9 @@ extern "C" const char* mcd_gemm_entry_point(const mcd_gemm_args* a) {
 }
 
 extern "C" size_t mcd_gemm_dynamic_smem(int arith) {
-    static_assert(MC_TC2_SMEM_BYTES == MC_TC_SMEM_BYTES, "both tensor-core kernels take the same dynamic shared memory");
-    return (arith == MCD_GEMM_TF32 || arith == MCD_GEMM_BF16 || arith == MCD_GEMM_F16) ? MC_TC_SMEM_BYTES : 0;
+    static_assert(MC_TC2_SMEM_BYTES >= MC_TC_SMEM_BYTES, "the pair kernels set the limit of both tensor-core families");
+    static_assert(MC_TC2_SMEM_BYTES + 64 <= 227 * 1024, "dynamic plus static shared memory of the pair kernel");
+    return (arith == MCD_GEMM_TF32 || arith == MCD_GEMM_BF16 || arith == MCD_GEMM_F16) ? MC_TC2_SMEM_BYTES : 0;
 }
 
 extern "C" int mcd_tensor_core_supported(int device, int arith) {

@@ -60,6 +60,7 @@ struct McTcParams {
     int splits;
     int half_tiles;  // the last `half_tiles` tiles are each issued as two 128-column work items (splits == 1 only)
     int wide;        // SM-pair kernel only: two 256-column tiles per work item
+    int staged;      // SM-pair kernel only: outputs leave through shared memory as whole row segments
 };
 
 __device__ __forceinline__ unsigned mc_smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }

@@ -22,7 +22,8 @@
 #define MC_TC2_A_BYTES (MC_TC_BM * 128)
 #define MC_TC2_B_BYTES (128 * 128)
 #define MC_TC2_STAGE_BYTES (MC_TC2_A_BYTES + MC_TC2_B_BYTES)
-#define MC_TC2_SMEM_BYTES (MC_TC2_STAGES * MC_TC2_STAGE_BYTES + 1024 + 256)
+#define MC_TC2_STAGING_PER_WARP 4096
+#define MC_TC2_SMEM_BYTES (MC_TC2_STAGES * MC_TC2_STAGE_BYTES + 1024 + 256 + MC_TC_EPILOGUE_WARPS * MC_TC2_STAGING_PER_WARP)
 
 __device__ __forceinline__ unsigned mc_cluster_ctarank() {
     unsigned r;
@@ -53,6 +54,16 @@ __device__ __forceinline__ void mc_tma_load_2d_pair(unsigned smem_dst, const McT
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_dst), "l"((unsigned long long)map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
         : "memory");
+}
+
+__device__ __forceinline__ void mc_st_shared_v4(unsigned addr, float a, float b, float c, float d) {
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__device__ __forceinline__ float4 mc_ld_shared_v4(unsigned addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
 }
 
 __device__ __forceinline__ void mc_umma_pair(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b, unsigned idesc,
@@ -343,6 +354,9 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
         const int col_begin = ((warp - 2) >> 2) * kColsPerWarp;
         const bool vec4 = (p.ldc & 3) == 0 && (((unsigned long long)p.c) & 15) == 0;
         const bool vec16 = (p.ldc16 & 7) == 0 && (((unsigned long long)p.c16) & 15) == 0;
+        // Staged stores need the aligned fast paths of both outputs; anything else takes the direct per-row stores.
+        const bool staged = p.staged != 0 && (p.c == nullptr || vec4) && (p.c16 == nullptr || vec16);
+        const unsigned stage_base = bars_base + 256 + (unsigned)(warp - 2) * MC_TC2_STAGING_PER_WARP;
         int acc = 0;
         unsigned full_phase = 0;  // bit r: parity of region r's tmem_full barrier
         bool ok = true;
@@ -351,7 +365,8 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
             decode(item, mp, nb, nsub, half);
             if (nsub == 0) continue;
             const int region0 = wide ? 0 : acc;
-            const int row = (2 * mp + (int)rank) * MC_TC_BM + quarter * 32 + lane;
+            const int row_base = (2 * mp + (int)rank) * MC_TC_BM + quarter * 32;
+            const int row = row_base + lane;
             // A whole tile: this warp's half of 256 columns. A half tile: this warp's half of its 128 columns,
             // which sit in accumulator columns 0..127.
             const int warp_cols = half < 0 ? kColsPerWarp : kColsPerWarp / 2;
@@ -381,11 +396,13 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
 #pragma unroll
                 for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {
                     const int col0 = n0 + tile_col_begin + chunk * 32;
-                    if (chunk * 32 < warp_cols && col0 < p.n && row < p.m) {
-                        float f[32];
+                    if (chunk * 32 >= warp_cols || col0 >= p.n) continue;  // warp-uniform
+                    float f[32];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[chunk][j]);
-                        if (col0 + 32 <= p.n) {
+                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[chunk][j]);
+                    const bool whole_chunk = col0 + 32 <= p.n;
+                    if (row < p.m) {
+                        if (whole_chunk) {
                             mc_epilogue32(f, (unsigned)row, (unsigned)col0, epi);
                         } else {
 #pragma unroll
@@ -393,9 +410,50 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                                 if (col0 + j < p.n) f[j] = mc_epilogue(f[j], (unsigned)row, (unsigned)(col0 + j), epi);
                             }
                         }
+                    }
+                    if (staged && whole_chunk) {
+                        // The 32 x 32 block goes through shared memory (16-byte pieces XOR-swizzled by row, so both
+                        // directions run at 4 wavefronts per 512 bytes) and leaves as whole 128-byte (FP32) or 64-byte
+                        // (16-bit) row segments: 4 or 8 complete rows per store instruction instead of 32 pieces.
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            mc_st_shared_v4(stage_base + lane * 128 + ((j ^ (lane & 7)) << 4), f[4 * j], f[4 * j + 1], f[4 * j + 2],
+                                            f[4 * j + 3]);
+                        }
+                        __syncwarp();
+                        if (p.c != nullptr) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                const int rr = q * 4 + (lane >> 3);
+                                const int cc = lane & 7;
+                                const float4 piece = mc_ld_shared_v4(stage_base + rr * 128 + ((cc ^ (rr & 7)) << 4));
+                                if (row_base + rr < p.m) {
+                                    *reinterpret_cast<float4*>(p.c + (long long)(row_base + rr) * p.ldc + col0 + cc * 4) = piece;
+                                }
+                            }
+                        }
+                        if (p.c16 != nullptr) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const int rr = q * 8 + (lane >> 2);
+                                const int cc = (lane & 3) * 2;
+                                const float4 lo = mc_ld_shared_v4(stage_base + rr * 128 + ((cc ^ (rr & 7)) << 4));
+                                const float4 hi = mc_ld_shared_v4(stage_base + rr * 128 + (((cc + 1) ^ (rr & 7)) << 4));
+                                uint4 pack;
+                                pack.x = mc_to_half2(lo.x, lo.y, p.c16_kind);
+                                pack.y = mc_to_half2(lo.z, lo.w, p.c16_kind);
+                                pack.z = mc_to_half2(hi.x, hi.y, p.c16_kind);
+                                pack.w = mc_to_half2(hi.z, hi.w, p.c16_kind);
+                                if (row_base + rr < p.m) {
+                                    *reinterpret_cast<uint4*>(p.c16 + (long long)(row_base + rr) * p.ldc16 + col0 + cc * 4) = pack;
+                                }
+                            }
+                        }
+                        __syncwarp();
+                    } else if (row < p.m) {
                         if (p.c != nullptr) {
                             float* out = p.c + (long long)row * p.ldc + col0;
-                            if (vec4 && col0 + 32 <= p.n) {
+                            if (vec4 && whole_chunk) {
 #pragma unroll
                                 for (int j = 0; j < 32; j += 4) {
                                     *reinterpret_cast<float4*>(out + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
@@ -409,7 +467,7 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                         }
                         if (p.c16 != nullptr) {
                             unsigned short* out16 = p.c16 + (long long)row * p.ldc16 + col0;
-                            if (vec16 && col0 + 32 <= p.n) {
+                            if (vec16 && whole_chunk) {
 #pragma unroll
                                 for (int j = 0; j < 32; j += 8) {
                                     uint4 pack;

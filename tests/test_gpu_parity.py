@@ -222,7 +222,7 @@ def _device_gemm(mc, arith, a, b, splits, b_transposed=False, half=None, variant
                     ("ldc", C.c_longlong), ("c16", C.c_void_p), ("c16_kind", C.c_int), ("ldc16", C.c_longlong),
                     ("splits", C.c_int), ("workspace", C.c_void_p), ("function", C.c_void_p), ("reduce_function", C.c_void_p),
                     ("epilogue_inputs", C.c_void_p * 6), ("num_epilogue_inputs", C.c_int), ("status", C.c_void_p),
-                    ("variant", C.c_int)]
+                    ("variant", C.c_int), ("has_epilogue", C.c_int)]
 
     m, k = a.shape
     n = b.shape[1]
