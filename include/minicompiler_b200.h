@@ -123,6 +123,9 @@ MC_EXPORT int mcb_graph_check_kernels(const void* graph, const char* options, in
 MC_EXPORT void mcb_uniform_values(float* out, long long count, unsigned long long seed, float lo, float hi);
 MC_EXPORT int mcb_split_k_splits(int m, int n, int k, int sm_count, int blocks_per_sm);
 MC_EXPORT int mcb_tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes);
+/* Columns per tile (256, 128 or 64) the tcgen05 path uses for an unsplit m x n x k problem; no counterpart in the
+ * reference, whose tensor-core kernel has one tile shape (src/cuda/matmul_tensor_core.cu:27-35). */
+MC_EXPORT int mcb_tensor_core_tile_n(int m, int n, int k, int sm_count, int elem_bytes);
 /* Name of the kernel `kernel_name` resolves to for this shape ("auto" -> "split_k" / "double_buffered");
  * NULL with a message in mc_last_error() for an unknown name. */
 MC_EXPORT const char* mcb_resolve_matmul_kernel(const char* kernel_name, int m, int n, int k, int sm_count);

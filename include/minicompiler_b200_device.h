@@ -156,6 +156,8 @@ typedef struct mcd_gemm_args {
     int num_epilogue_inputs;
     unsigned int* status; /* device word: a kernel that gives up a bounded wait ORs an error code in */
     int variant;          /* tuning variant, 0 = default */
+    int tile_n;           /* tensor-core arithmetic: columns per tile, 0 or 256 = default, 128 or 64 = narrow tiles
+                             for small unsplit problems (one-CTA kernel) */
     int has_epilogue;     /* non-zero when the launch carries a generated epilogue; set it before asking for the
                              entry point as well, kernel selection depends on it */
 } mcd_gemm_args;

@@ -20,6 +20,7 @@ from .api import (  # noqa: F401
     shard_dims,
     split_k_splits,
     tensor_core_splits,
+    tensor_core_tile_n,
     uniform_values,
 )
 
@@ -34,5 +35,6 @@ __all__ = [
     "shard_dims",
     "split_k_splits",
     "tensor_core_splits",
+    "tensor_core_tile_n",
     "uniform_values",
 ]

@@ -79,6 +79,7 @@ def lib() -> C.CDLL:
         "mcb_uniform_values": (None, [C.POINTER(C.c_float), i64, C.c_ulonglong, C.c_float, C.c_float]),
         "mcb_split_k_splits": (i32, [i32, i32, i32, i32, i32]),
         "mcb_tensor_core_splits": (i32, [i32, i32, i32, i32, i32]),
+        "mcb_tensor_core_tile_n": (i32, [i32, i32, i32, i32, i32]),
         "mcb_resolve_matmul_kernel": (cp, [cp, i32, i32, i32, i32]),
         "mcd_launch_count": (C.c_ulonglong, []),
     }
@@ -356,6 +357,10 @@ def split_k_splits(m: int, n: int, k: int, sm_count: int, blocks_per_sm: int = 2
 
 def tensor_core_splits(m: int, n: int, k: int, sm_count: int, elem_bytes: int = 2) -> int:
     return lib().mcb_tensor_core_splits(m, n, k, sm_count, elem_bytes)
+
+
+def tensor_core_tile_n(m: int, n: int, k: int, sm_count: int, elem_bytes: int = 2) -> int:
+    return lib().mcb_tensor_core_tile_n(m, n, k, sm_count, elem_bytes)
 
 
 def resolve_matmul_kernel(name: str, m: int, n: int, k: int, sm_count: int) -> str:

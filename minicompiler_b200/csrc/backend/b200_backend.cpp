@@ -606,6 +606,7 @@ private:
             g.ldc16 = half_pitch(step.n);
         }
         g.splits = step.splits;
+        g.tile_n = step.tile_n;
         g.workspace = step.splits > 1 ? workspace : nullptr;
         g.variant = options_.gemm_variant;
         if (is_tensor_core(step.kernel)) {

@@ -64,10 +64,27 @@ int split_k_splits(int m, int n, int k, int sm_count, int blocks_per_sm) {
     return static_cast<int>(std::max<std::int64_t>(splits, 1));
 }
 
+int tensor_core_tile_n(int m, int n, int k, int sm_count, int elem_bytes) {
+    const std::int64_t rows = (static_cast<std::int64_t>(m) + 127) / 128;
+    const std::int64_t sms = sm_count;
+    if (5 * rows * ((static_cast<std::int64_t>(n) + 255) / 256) >= 4 * sms) return 256;
+    // A problem too small to fill the SMs with 128 x 256 tiles: narrower tiles in one launch beat a K split plus
+    // its reduction pass as long as the extra operand traffic stays small (every tile re-reads its 128 rows of A).
+    const std::int64_t block_k = 128 / elem_bytes;
+    const std::int64_t k_blocks = (k + block_k - 1) / block_k;
+    for (int width : {128, 64}) {
+        const std::int64_t tiles = rows * ((static_cast<std::int64_t>(n) + width - 1) / width);
+        const std::int64_t traffic = tiles * k_blocks * (128 * 128 + width * 128);
+        if (5 * tiles >= 4 * sms || width == 64) return traffic <= kNarrowTileTrafficLimit && 2 * tiles >= sms ? width : 256;
+    }
+    return 256;
+}
+
 int tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes) {
     const std::int64_t tiles = ((static_cast<std::int64_t>(m) + 127) / 128) * ((static_cast<std::int64_t>(n) + 255) / 256);
     const std::int64_t sms = sm_count;
     if (5 * tiles >= 4 * sms) return 1;
+    if (tensor_core_tile_n(m, n, k, sm_count, elem_bytes) != 256) return 1;
     const std::int64_t block_k = 128 / elem_bytes;
     const std::int64_t k_blocks = (k + block_k - 1) / block_k;
     std::int64_t splits = std::min<std::int64_t>(sms / tiles, k_blocks / 4);  // at least 4 K blocks per work item
@@ -189,6 +206,9 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
                   : kernel == MatmulKernel::TensorCoreF16  ? Arith::F16
                                                            : Arith::F32;
         s.splits = matmul_splits(kernel, s.m, s.n, s.k, sm_count);
+        if (is_tensor_core(kernel)) {
+            s.tile_n = tensor_core_tile_n(s.m, s.n, s.k, sm_count, kernel == MatmulKernel::TensorCoreTf32 ? 4 : 2);
+        }
         // TF32 always takes the [n,k] copy of B: with 32-bit elements the MN-major shared-memory form did not
         // yield correct products on B200, while the K-major form does. 16-bit operands work in both forms.
         s.rhs_transposed = is_tensor_core(kernel) && (rhs_transposed || kernel == MatmulKernel::TensorCoreTf32);
@@ -448,6 +468,7 @@ std::string describe(const Graph& graph, const LoweredGraph& lowered) {
         } else {
             os << "matmul " << graph.node(s.matmul).name << " " << s.m << "x" << s.n << "x" << s.k << " kernel="
                << matmul_kernel_name(s.kernel) << " splits=" << s.splits;
+            if (s.tile_n != 256) os << " tile_n=" << s.tile_n;
             if (s.rhs_transposed) os << " rhs=transposed";
             if (s.has_epilogue) os << " epilogue=" << graph.node(s.result).name << "(" << s.program.num_ops() << " ops)";
         }

@@ -47,6 +47,10 @@ bool uses_split_k(MatmulKernel kernel);
 int split_k_splits(int m, int n, int k, int sm_count, int blocks_per_sm = 2);
 // The rule for the tcgen05 kernels: 128x256 tiles, one persistent CTA per SM.
 int tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes);
+// Columns per tile of the one-CTA tcgen05 kernel for this problem: 256, or 128 / 64 for problems that neither fill
+// the SMs with 128 x 256 tiles nor are worth a K split (operand traffic of the narrow tiling at most this many bytes).
+constexpr std::int64_t kNarrowTileTrafficLimit = 128LL << 20;
+int tensor_core_tile_n(int m, int n, int k, int sm_count, int elem_bytes);
 MatmulKernel resolve_matmul_kernel(MatmulKernel kernel, int m, int n, int k, int sm_count);
 int matmul_splits(MatmulKernel kernel, int m, int n, int k, int sm_count);
 std::size_t matmul_workspace_bytes(MatmulKernel kernel, int m, int n, int splits);
@@ -108,6 +112,7 @@ struct Step {
     MatmulKernel kernel = MatmulKernel::DoubleBuffered;  // what matmul_kernels() reports
     Arith arith = Arith::F32;
     int splits = 1;
+    int tile_n = 256;  // tensor-core kernels: columns per tile (tensor_core_tile_n)
     bool rhs_transposed = false;
     bool has_epilogue = false;
     std::vector<EpilogueOperand> operands;  // indexed by the program's load numbers (entry for the matmul unused)

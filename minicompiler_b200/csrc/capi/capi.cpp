@@ -533,6 +533,10 @@ int mcb_tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes) {
     return cuda::tensor_core_splits(m, n, k, sm_count, elem_bytes);
 }
 
+int mcb_tensor_core_tile_n(int m, int n, int k, int sm_count, int elem_bytes) {
+    return cuda::tensor_core_tile_n(m, n, k, sm_count, elem_bytes);
+}
+
 const char* mcb_resolve_matmul_kernel(const char* kernel_name, int m, int n, int k, int sm_count) {
     Result<cuda::MatmulKernel> kernel = cuda::matmul_kernel_from_name(kernel_name != nullptr ? kernel_name : "");
     if (!kernel.ok()) {

@@ -262,17 +262,18 @@ int tc_splits(const mcd_gemm_args* a) {
     return (k_blocks + per - 1) / per;
 }
 
-// Whether the launch goes to the SM-pair kernel: unsplit problems whose 256 x 256 pair tiles give every SM pair
-// at least kPairMinWaves tiles; variant bit 8 forces it for any unsplit problem, bit 4 turns it off.
-constexpr int kPairMinWaves = 1;
+// Whether the launch goes to the SM-pair kernel: unsplit problems with at least half a wave of 256 x 256 pair
+// tiles (2048^3: 64 tiles on 74 pairs, 739 against 653 TFLOP/s); variant bit 8 forces it for any unsplit problem,
+// bit 4 turns it off.
 bool tc_uses_pairs(const mcd_gemm_args* a) {
     if (a->arith == MCD_GEMM_F32 || tc_splits(a) != 1 || (a->variant & 4) != 0) return false;
+    if (a->tile_n != 0 && a->tile_n != MC_TC_BN) return false;
     if (a->arith == MCD_GEMM_TF32 && a->b_transposed == 0) return false;
     if ((a->variant & 8) != 0) return true;
     const long long tiles_m = (a->m + MC_TC_BM - 1) / MC_TC_BM;
     if (tiles_m % 2 != 0 && tiles_m < 9) return false;  // the odd row block's partner would idle
     const long long items = ((tiles_m + 1) / 2) * ((a->n + MC_TC_BN - 1) / MC_TC_BN);
-    return items >= static_cast<long long>(kPairMinWaves) * (sm_count_of_current_device() / 2);
+    return 2 * items >= sm_count_of_current_device() / 2;  // from half a wave of pair tiles upwards
 }
 
 // Whether the SM-pair kernel takes two 256-column tiles per work item.
@@ -302,6 +303,8 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
         return fail("mcd_gemm: tensor-core operands need 16-byte aligned bases and row pitches");
     }
     if (tf32 && !b_k_major) return fail("mcd_gemm: TF32 reads B as a [n,k] copy only (set b_transposed)");
+    const int tile_n = a->tile_n == 0 ? MC_TC_BN : a->tile_n;
+    if (tile_n != 64 && tile_n != 128 && tile_n != MC_TC_BN) return fail("mcd_gemm: tile_n must be 0, 64, 128 or 256");
     const int k_blocks = (a->k + block_k - 1) / block_k;
     int splits = std::max(1, std::min(a->splits, k_blocks));
     const int per = (k_blocks + splits - 1) / splits;
@@ -320,7 +323,7 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     if (b_k_major) {
         // A CTA of the pair kernel keeps 128 of the tile's 256 columns.
         if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_b), type, elem, a->b, a->k, a->n, a->ldb, block_k,
-                                pairs ? MC_TC_BN / 2 : MC_TC_BN)) {
+                                pairs ? MC_TC_BN / 2 : tile_n)) {
             return rc;
         }
     } else {
@@ -341,15 +344,17 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     p.n = a->n;
     p.k = a->k;
     p.idesc = instruction_descriptor(a->arith, b_k_major);
+    p.idesc = (p.idesc & ~(0x3Fu << 17)) | (static_cast<unsigned>(tile_n >> 3) << 17);
+    p.tile_n = tile_n;
     p.k_blocks_per_split = per;
     p.splits = splits;
     p.wide = 0;
     p.staged = (a->variant & 128) == 0 ? 1 : 0;
     // Tiles that do not fill the last wave of CTAs are cut in two when both halves of all of them fit in one wave.
     const int sms = sm_count_of_current_device();
-    const int all_tiles = ((a->m + MC_TC_BM - 1) / MC_TC_BM) * ((a->n + MC_TC_BN - 1) / MC_TC_BN);
+    const int all_tiles = ((a->m + MC_TC_BM - 1) / MC_TC_BM) * ((a->n + tile_n - 1) / tile_n);
     const int tail = all_tiles % sms;
-    p.half_tiles = (splits == 1 && (a->variant & 2) == 0 && tail > 0 && 2 * tail <= sms) ? tail : 0;
+    p.half_tiles = (splits == 1 && tile_n == MC_TC_BN && (a->variant & 2) == 0 && tail > 0 && 2 * tail <= sms) ? tail : 0;
     McEpilogueArgs epi = epilogue_args(a);
 
     if (pairs) {

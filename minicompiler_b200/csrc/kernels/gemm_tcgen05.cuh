@@ -61,6 +61,8 @@ struct McTcParams {
     int half_tiles;  // the last `half_tiles` tiles are each issued as two 128-column work items (splits == 1 only)
     int wide;        // SM-pair kernel only: two 256-column tiles per work item
     int staged;      // SM-pair kernel only: outputs leave through shared memory as whole row segments
+    int tile_n;      // one-CTA kernel only: columns per tile, 256 (default), 128 or 64; narrow tiles let a small
+                     // problem fill the SMs in one launch instead of splitting K (idesc carries the same N)
 };
 
 __device__ __forceinline__ unsigned mc_smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -222,7 +224,8 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
     const int lane = threadIdx.x & 31;
 
     const int tiles_m = (p.m + MC_TC_BM - 1) / MC_TC_BM;
-    const int tiles_n = (p.n + MC_TC_BN - 1) / MC_TC_BN;
+    const int bn = p.tile_n;  // columns per tile; accumulators stay MC_TC_BN TMEM columns apart
+    const int tiles_n = (p.n + bn - 1) / bn;
     const int k_blocks = (p.k + kBlockK - 1) / kBlockK;
     const int items = (tiles_m * tiles_n + p.half_tiles) * p.splits;
 
@@ -267,14 +270,15 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
                     const unsigned full = bar_full + 8 * stage;
                     const unsigned a_dst = tiles_base + stage * MC_TC_STAGE_BYTES;
                     const unsigned b_dst = a_dst + MC_TC_A_BYTES;
-                    mc_mbar_expect_tx(full, MC_TC_STAGE_BYTES);
+                    mc_mbar_expect_tx(full, (unsigned)(MC_TC_A_BYTES + bn * 128));
                     mc_tma_load_2d(a_dst, &map_a, full, kb * kBlockK, mb * MC_TC_BM);
                     if (kBIsKMajor) {
-                        mc_tma_load_2d(b_dst, &map_b, full, kb * kBlockK, nb * MC_TC_BN);
+                        mc_tma_load_2d(b_dst, &map_b, full, kb * kBlockK, nb * bn);  // the map's box holds bn rows
                     } else {
 #pragma unroll
                         for (int j = 0; j < MC_TC_BN / kAtomN; ++j) {
-                            mc_tma_load_2d(b_dst + j * (kBlockK * 128), &map_b, full, nb * MC_TC_BN + j * kAtomN,
+                            if (j * kAtomN >= bn) break;
+                            mc_tma_load_2d(b_dst + j * (kBlockK * 128), &map_b, full, nb * bn + j * kAtomN,
                                            kb * kBlockK);
                         }
                     }
@@ -363,7 +367,7 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
         // ---------------------------------------------------------------- epilogue
         const int quarter = warp & 3;  // the TMEM lanes this warp may touch: [32*quarter, +32)
         // Two warps share each lane quarter and take one half of the tile's columns each.
-        constexpr int kColsPerWarp = MC_TC_BN / (MC_TC_EPILOGUE_WARPS / 4);
+        const int kColsPerWarp = bn / (MC_TC_EPILOGUE_WARPS / 4);
         const int col_begin = ((warp - 2) >> 2) * kColsPerWarp;
         int acc = 0;
         unsigned acc_phase = 0;
@@ -377,7 +381,7 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = mb * MC_TC_BM + quarter * 32 + lane;
-            const int n0 = nb * MC_TC_BN;
+            const int n0 = nb * bn;
             float* dst = partial ? p.workspace + (long long)split * p.m * p.n : p.c;
             const long long ld = partial ? (long long)p.n : p.ldc;
             const bool vec4 = (ld & 3) == 0 && (((unsigned long long)dst) & 15) == 0;

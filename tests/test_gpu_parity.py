@@ -211,7 +211,7 @@ def _torch():
     return torch
 
 
-def _device_gemm(mc, arith, a, b, splits, b_transposed=False, half=None, variant=0):
+def _device_gemm(mc, arith, a, b, splits, b_transposed=False, half=None, variant=0, tile_n=0):
     """Calls mcd_gemm directly with device buffers held by torch; C is pre-filled with NaN."""
     torch = _torch()
     lib = mc.lib()
@@ -222,7 +222,7 @@ def _device_gemm(mc, arith, a, b, splits, b_transposed=False, half=None, variant
                     ("ldc", C.c_longlong), ("c16", C.c_void_p), ("c16_kind", C.c_int), ("ldc16", C.c_longlong),
                     ("splits", C.c_int), ("workspace", C.c_void_p), ("function", C.c_void_p), ("reduce_function", C.c_void_p),
                     ("epilogue_inputs", C.c_void_p * 6), ("num_epilogue_inputs", C.c_int), ("status", C.c_void_p),
-                    ("variant", C.c_int), ("has_epilogue", C.c_int)]
+                    ("variant", C.c_int), ("tile_n", C.c_int), ("has_epilogue", C.c_int)]
 
     m, k = a.shape
     n = b.shape[1]
@@ -259,6 +259,7 @@ def _device_gemm(mc, arith, a, b, splits, b_transposed=False, half=None, variant
     args.c, args.ldc, args.splits, args.workspace = tc.data_ptr(), n, splits, ws.data_ptr()
     args.status = status.data_ptr()
     args.variant = variant
+    args.tile_n = tile_n
     lib.mcd_gemm.restype = C.c_int
     lib.mcd_last_error.restype = C.c_char_p
     stream = torch.cuda.current_stream().cuda_stream
@@ -299,6 +300,25 @@ def test_tensor_core_kernel_direct(mc, oracle, name, arith, half, u, sub, layout
         for splits in [1, 3]:
             got = _device_gemm(mc, arith, a, b, splits, b_transposed=layout, half=half)
             check_bound(got, exact, abs_dot, k, u, sub, f"{name} {m}x{k}x{n} splits={splits} transposed={layout}")
+
+
+@pytest.mark.parametrize("layout", [False, True])
+@pytest.mark.parametrize("name,arith,half,u,sub", TC_KINDS)
+def test_tensor_core_narrow_tiles_direct(mc, oracle, name, arith, half, u, sub, layout):
+    """128 x 128 and 128 x 64 tiles of the one-CTA kernel give the bits of its 128 x 256 tiles."""
+    if half is None and not layout:
+        pytest.skip("TF32 reads B as a [n,k] copy only")
+    for m, k, n in [(128, 64, 64), (256, 512, 512), (300, 1004, 36), (33, 264, 72), (1024, 1024, 1024), (130, 200, 1000)]:
+        if half is None and (k % 4 or n % 4):
+            continue
+        a = oracle.uniform_values(m * k, 1, -1, 1).reshape(m, k)
+        b = oracle.uniform_values(k * n, 2, -1, 1).reshape(k, n)
+        whole = _device_gemm(mc, arith, a, b, 1, b_transposed=layout, half=half, variant=4)
+        for tile_n in (128, 64):
+            got = _device_gemm(mc, arith, a, b, 1, b_transposed=layout, half=half, variant=4, tile_n=tile_n)
+            assert np.array_equal(got, whole), f"{name} {m}x{k}x{n} transposed={layout} tile_n={tile_n}"
+        exact, abs_dot = exact_and_abs(a, b)
+        check_bound(whole, exact, abs_dot, k, u, sub, f"{name} {m}x{k}x{n} transposed={layout}")
 
 
 @pytest.mark.parametrize("layout", [False, True])

@@ -307,7 +307,13 @@ def test_split_rule_on_148_sms_for_the_configs(mc):
     assert mc.split_k_splits(256, 2048, 512, 148) == 4
     assert mc.split_k_splits(8192, 4096, 1024, 148) == 1
     # tcgen05 rule (128x256 tiles, one CTA per SM)
-    assert mc.tensor_core_splits(1024, 1024, 1024, 148) == 4
+    assert mc.tensor_core_splits(1024, 1024, 1024, 148) == 1  # narrow tiles instead: 8 x 16 tiles of 128 x 64
+    assert mc.tensor_core_tile_n(1024, 1024, 1024, 148) == 64
+    assert mc.tensor_core_tile_n(1024, 1024, 65536, 148) == 256  # too much operand traffic: split K
+    assert mc.tensor_core_tile_n(16, 8192, 8192, 148) == 256
+    assert mc.tensor_core_tile_n(8192, 8192, 8192, 148) == 256
+    assert mc.tensor_core_tile_n(512, 2048, 512, 148) == 64
+    assert mc.tensor_core_tile_n(256, 2048, 512, 148) == 256  # 64 narrow tiles would leave most SMs idle: split K
     assert mc.tensor_core_splits(1024, 1024, 65536, 148) == 4
     assert mc.tensor_core_splits(16, 8192, 8192, 148) == 4
     assert mc.tensor_core_splits(8192, 8192, 8192, 148) == 1
