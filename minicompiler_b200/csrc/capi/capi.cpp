@@ -16,6 +16,8 @@
 #include <fstream>
 #include <memory>
 #include <sstream>
+#include <mutex>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -493,6 +495,23 @@ int mcb_graph_check_kernels(const void* graph, const char* options, int sm_count
         g_error = lowered.error().message;
         return 1;
     }
+    // Every distinct text is compiled once. Of a tensor-core kernel family, which holds ten entry points, one
+    // entry point of each body (one CTA per tile, SM pair, SM pair with two tiles) is compiled, as at run time.
+    static std::set<std::string> seen;  // texts that compiled, for the life of the process
+    static std::mutex seen_mutex;
+    auto compile_once = [&](const std::string& text) -> bool {
+        {
+            std::lock_guard<std::mutex> lock(seen_mutex);
+            if (seen.count(text) != 0) return true;
+        }
+        if (mcd_jit_compile_only(text.c_str(), "--fmad=false", nullptr) != 0) {
+            g_error = mcd_last_error();
+            return false;
+        }
+        std::lock_guard<std::mutex> lock(seen_mutex);
+        seen.insert(text);
+        return true;
+    };
     for (const cuda::Step& step : lowered->steps) {
         std::string source;
         if (step.kind == cuda::Step::Kind::Elementwise) {
@@ -510,13 +529,19 @@ int mcb_graph_check_kernels(const void* graph, const char* options, int sm_count
         } else if (step.has_epilogue) {
             source = cuda::generate_epilogue_source(g, step) +
                      mcd_gemm_source(step.splits > 1 ? -1 : static_cast<int>(step.arith));
+            if (step.splits == 1 && step.arith != cuda::Arith::F32) {
+                const bool tf32 = step.arith == cuda::Arith::Tf32;
+                for (const char* entry : {tf32 ? "mc_gemm_tc_tf32_bk" : "mc_gemm_tc_h16_bmn",
+                                          tf32 ? "mc_gemm_tc2_tf32_bk" : "mc_gemm_tc2_h16_bk",
+                                          tf32 ? "mc_gemm_tc2w_tf32_bk" : "mc_gemm_tc2w_h16_bmn"}) {
+                    if (!compile_once(std::string("#define MC_SINGLE_ENTRY 1\n#define MC_ONLY_") + entry + " 1\n" + source)) return 1;
+                }
+                continue;
+            }
         } else {
             continue;
         }
-        if (mcd_jit_compile_only(source.c_str(), "--fmad=false", nullptr) != 0) {
-            g_error = mcd_last_error();
-            return 1;
-        }
+        if (!compile_once(source)) return 1;
     }
     return 0;
 }
