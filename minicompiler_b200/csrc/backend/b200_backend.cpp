@@ -480,6 +480,8 @@ private:
             const Step& step = lowered_.steps[i];
             if (step.kind == Step::Kind::Elementwise) {
                 MC_TRY(add_elementwise(step));
+            } else if (step.kind == Step::Kind::Reduce) {
+                MC_TRY(add_reduce(step));
             } else {
                 MC_TRY(add_matmul(step, workspace));
             }
@@ -566,6 +568,41 @@ private:
         for (NodeId in : step.inputs) {
             launch->pointers.push_back(address(in, kRepF32));
             launch->advances.push_back(graph_.node(in).type.num_elements() == n ? 1 : 0);
+        }
+        for (void*& p : launch->pointers) launch->params.push_back(&p);
+        launch->params.push_back(&launch->count);
+        launches_.push_back(std::move(launch));
+        return Status();
+    }
+
+    // A row reduction with its elementwise prologue: one generated kernel, a warp or a block per row.
+    Status add_reduce(const Step& step) {
+        const Node& node = graph_.node(step.result);
+        std::vector<Shape> shapes;
+        for (NodeId in : step.inputs) shapes.push_back(graph_.node(in).type.shape);
+        const RowReduceKernel kernel = generate_row_reduce_kernel(step.reduce_op, step.program, shapes, step.reduce_shape);
+
+        auto launch = std::make_unique<Launch>();
+        launch->kind = Launch::Kind::Elementwise;
+        double ms = 0.0;
+        if (mcd_jit_kernel(options_.device, kernel.source.c_str(), kRowReduceKernelName, "--fmad=false", &launch->function, &ms) != 0) {
+            return Error{std::string("compiling the kernel of '") + node.name + "' failed: " + mcd_last_error()};
+        }
+        jit_ms_ += ms;
+        sources_.push_back(kernel.source);
+
+        const std::size_t rows = node.type.num_elements();
+        launch->count = static_cast<unsigned>(rows);
+        int blocks_per_sm = 0;
+        MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(kRowReduceBlock), 0, &blocks_per_sm));
+        const std::size_t wanted = (rows + kernel.rows_per_block - 1) / kernel.rows_per_block;
+        const std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
+        launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(wanted, resident)));
+        launch->pointers.push_back(address(step.result, kRepF32));
+        launch->advances.push_back(0);
+        for (NodeId in : step.inputs) {
+            launch->pointers.push_back(address(in, kRepF32));
+            launch->advances.push_back(0);
         }
         for (void*& p : launch->pointers) launch->params.push_back(&p);
         launch->params.push_back(&launch->count);

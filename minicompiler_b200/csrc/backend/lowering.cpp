@@ -216,12 +216,44 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
         return s;
     };
 
+    // An elementwise producer that only a row reduction reads is evaluated inside the reduction kernel and never
+    // written out.
+    std::vector<NodeId> absorbed_by(count, kNoNode);  // producer -> reduction
+    for (std::size_t i = 0; i < count; ++i) {
+        const Node& rn = graph.node(static_cast<NodeId>(i));
+        if (!is_row_reduce(rn.op)) continue;
+        const NodeId p = rn.inputs[0];
+        const Node& pn = graph.node(p);
+        const auto pi = static_cast<std::size_t>(p);
+        const bool elementwise_like = is_elementwise(pn.op) || pn.op == OpKind::FusedElementwise;
+        if (elementwise_like && !graph.is_output(p) && users[pi].size() == 1 && carries[pi] == kNoNode) {
+            absorbed_by[pi] = static_cast<NodeId>(i);
+        }
+    }
+
     std::vector<std::int32_t> step_of(count, -1);
     for (std::size_t i = 0; i < count; ++i) {
         const auto id = static_cast<NodeId>(i);
         const Node& n = graph.node(id);
         if (!is_compute(n.op)) continue;
-        if (n.op == OpKind::MatMul) {
+        if (absorbed_by[i] != kNoNode) continue;  // evaluated inside its reduction
+        if (is_row_reduce(n.op)) {
+            Step s;
+            s.kind = Step::Kind::Reduce;
+            s.result = id;
+            s.reduce_op = n.op;
+            const NodeId p = n.inputs[0];
+            const Node& pn = graph.node(p);
+            s.reduce_shape = pn.type.shape;
+            if (absorbed_by[static_cast<std::size_t>(p)] == id) {
+                s.program = pn.op == OpKind::FusedElementwise ? *pn.fused : single_op_program(pn.op);
+                s.inputs = pn.inputs;
+            } else {
+                s.program.instrs.push_back(FusedInstr::load(0));
+                s.inputs = {p};
+            }
+            out.steps.push_back(std::move(s));
+        } else if (n.op == OpKind::MatMul) {
             if (folded_into[i] != kNoNode) continue;  // emitted with its consumer
             out.steps.push_back(make_matmul_step(id));
         } else if (carries[i] != kNoNode) {
@@ -253,7 +285,7 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
     // What form each value is read in.
     auto need = [&](NodeId v, Rep rep) { out.needs[static_cast<std::size_t>(v)][rep] = true; };
     for (const Step& s : out.steps) {
-        if (s.kind == Step::Kind::Elementwise) {
+        if (s.kind != Step::Kind::Matmul) {
             for (NodeId in : s.inputs) need(in, kRepF32);
             continue;
         }
@@ -279,9 +311,10 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
         const Node& n = graph.node(id);
         auto& needs = out.needs[i];
         if (is_compute(n.op)) {
-            if (step_of[i] < 0) continue;  // a folded matmul has no value of its own
-            for (Rep rep : {kRepHalfT, kRepF32T}) {
+            if (step_of[i] < 0) continue;  // a folded matmul or an absorbed producer has no value of its own
+            for (Rep rep : {kRepHalf, kRepHalfT, kRepF32T}) {
                 if (!needs[rep]) continue;
+                if (rep == kRepHalf && !is_row_reduce(n.op)) continue;  // written by the producing kernel itself
                 needs[kRepF32] = true;
                 out.after_step[static_cast<std::size_t>(step_of[i])].push_back({id, rep});
             }
@@ -301,7 +334,7 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
     for (Step& s : out.steps) {
         const auto& needs = out.needs[static_cast<std::size_t>(s.result)];
         s.write_f32 = needs[kRepF32];
-        s.write_half = needs[kRepHalf] ? out.half_kind : HalfKind::None;
+        s.write_half = needs[kRepHalf] && s.kind != Step::Kind::Reduce ? out.half_kind : HalfKind::None;
     }
 
     // Launch count and the shared split-K workspace.
@@ -333,7 +366,7 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
                 ps.defines.push_back(value_index(s.result, static_cast<Rep>(rep)));
             }
         }
-        if (s.kind == Step::Kind::Elementwise) {
+        if (s.kind != Step::Kind::Matmul) {
             for (NodeId in : s.inputs) ps.reads.push_back(value_index(in, kRepF32));
         } else {
             const bool half = s.arith == Arith::Bf16 || s.arith == Arith::F16;
@@ -465,6 +498,9 @@ std::string describe(const Graph& graph, const LoweredGraph& lowered) {
         os << i << ": ";
         if (s.kind == Step::Kind::Elementwise) {
             os << "elementwise " << graph.node(s.result).name << " ops=" << s.program.num_ops();
+        } else if (s.kind == Step::Kind::Reduce) {
+            os << op_name(s.reduce_op) << " " << graph.node(s.result).name << " rows of " << s.reduce_shape.back()
+               << " prologue_ops=" << s.program.num_ops();
         } else {
             os << "matmul " << graph.node(s.matmul).name << " " << s.m << "x" << s.n << "x" << s.k << " kernel="
                << matmul_kernel_name(s.kernel) << " splits=" << s.splits;

@@ -10,6 +10,7 @@
 // never goes to memory in FP32 and one launch disappears.
 
 #include "backend/eltwise_codegen.hpp"
+#include "backend/reduce_codegen.hpp"
 #include "core/ir.hpp"
 #include "core/plan.hpp"
 
@@ -96,14 +97,20 @@ struct EpilogueOperand {
 };
 
 struct Step {
-    enum class Kind { Elementwise, Matmul };
+    enum class Kind { Elementwise, Matmul, Reduce };
     Kind kind = Kind::Elementwise;
     NodeId result = kNoNode;  // the node whose value this step defines
 
     // Elementwise: `program` over `inputs`. Matmul with a folded consumer: `program` is the
     // consumer's program, loads of `matmul` read the accumulator, other loads read `operands`.
+    // Reduce: `program` over `inputs` is evaluated per element of `reduce_shape` (the identity program,
+    // or the program of an elementwise producer that only this reduction reads) and each row of the last
+    // dimension is combined with `reduce_op`.
     FusedProgram program;
     std::vector<NodeId> inputs;
+
+    OpKind reduce_op = OpKind::RowSum;
+    Shape reduce_shape;
 
     NodeId matmul = kNoNode;
     NodeId lhs = kNoNode;

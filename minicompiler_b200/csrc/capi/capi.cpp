@@ -444,6 +444,14 @@ int mcb_graph_emit_cuda(const void* graph, const char* options, char* out, int s
     std::string text;
     for (std::size_t i = 0; i < g.num_nodes(); ++i) {
         const Node& n = g.node(static_cast<NodeId>(i));
+        if (is_row_reduce(n.op)) {  // the node on its own: identity prologue
+            FusedProgram identity;
+            identity.instrs.push_back(FusedInstr::load(0));
+            const Shape& in_shape = g.node(n.inputs[0]).type.shape;
+            text += "// node %" + std::to_string(i) + " '" + n.name + "' : " + to_string(n.type) + "\n";
+            text += cuda::generate_row_reduce_kernel(n.op, identity, {in_shape}, in_shape).source + "\n";
+            continue;
+        }
         if (!is_elementwise(n.op) && n.op != OpKind::FusedElementwise) continue;
         std::vector<Shape> shapes;
         for (NodeId in : n.inputs) shapes.push_back(g.node(in).type.shape);
@@ -526,6 +534,10 @@ int mcb_graph_check_kernels(const void* graph, const char* options, int sm_count
             const TensorType& type = g.node(step.result).type;
             if (step.write_half != cuda::HalfKind::None && type.shape.size() == 2) eo.half_pitch = cuda::half_pitch(type.shape[1]);
             source = cuda::generate_elementwise_kernel(step.program, shapes, type.shape, eo).source;
+        } else if (step.kind == cuda::Step::Kind::Reduce) {
+            std::vector<Shape> shapes;
+            for (NodeId in : step.inputs) shapes.push_back(g.node(in).type.shape);
+            source = cuda::generate_row_reduce_kernel(step.reduce_op, step.program, shapes, step.reduce_shape).source;
         } else if (step.has_epilogue) {
             source = cuda::generate_epilogue_source(g, step) +
                      mcd_gemm_source(step.splits > 1 ? -1 : static_cast<int>(step.arith));

@@ -83,6 +83,7 @@ constexpr OpRow kOps[] = {
     {OpKind::Sub, "sub", 2, true},          {OpKind::Mul, "mul", 2, true},
     {OpKind::Div, "div", 2, true},          {OpKind::MatMul, "matmul", 2, true},
     {OpKind::FusedElementwise, "fused", -1, false},
+    {OpKind::RowSum, "row_sum", 1, true},   {OpKind::RowMax, "row_max", 1, true},
 };
 
 const OpRow* row_of(OpKind op) {
@@ -152,6 +153,12 @@ Result<TensorType> infer_result_type(OpKind op, const std::vector<TensorType>& o
         }
     }
     if (is_unary_elementwise(op)) return operands[0];
+    if (is_row_reduce(op)) {
+        Shape shape = operands[0].shape;
+        if (shape.empty()) return Error{std::string(op_name(op)) + " expects an operand of rank 1 or more, got " + to_string(shape)};
+        shape.back() = 1;
+        return TensorType(std::move(shape));
+    }
     if (is_binary_elementwise(op)) {
         Result<Shape> shape = broadcast_shapes(operands[0].shape, operands[1].shape);
         if (!shape.ok()) return Error{std::string(op_name(op)) + ": " + shape.error().message};
@@ -310,7 +317,7 @@ Result<NodeId> Graph::add_constant(std::string name, TensorType type,
 }
 
 Result<NodeId> Graph::add_op(OpKind op, std::vector<NodeId> inputs, std::string name) {
-    if (!is_elementwise(op) && op != OpKind::MatMul) {
+    if (!is_elementwise(op) && op != OpKind::MatMul && !is_row_reduce(op)) {
         return Error{std::string("add_op cannot create '") + op_name(op) + "' nodes"};
     }
     MC_TRY(operands_exist(inputs));
@@ -455,6 +462,8 @@ GraphStats compute_stats(const Graph& graph) {
                 s.elementwise_ops += n.fused->num_ops();
             } else if (n.op == OpKind::MatMul) {
                 ++s.matmuls;
+            } else if (is_row_reduce(n.op)) {
+                ++s.reductions;
             } else {
                 ++s.elementwise_ops;
             }

@@ -71,6 +71,12 @@ enum class OpKind : std::uint8_t {
     Div,
     MatMul,
     FusedElementwise,
+    // Row reductions (an extension; the reference's IR has none, README.md:561-562): the last dimension of the
+    // operand collapses to extent 1, every other extent is kept, so the result broadcasts back against the operand.
+    // row_sum is defined as the sum accumulated in double and rounded once; row_max as the largest element (the
+    // operand is assumed free of NaN).
+    RowSum,
+    RowMax,
 };
 
 const char* op_name(OpKind op);
@@ -79,6 +85,7 @@ std::optional<OpKind> op_from_name(std::string_view name);
 bool is_unary_elementwise(OpKind op);
 bool is_binary_elementwise(OpKind op);
 inline bool is_elementwise(OpKind op) { return is_unary_elementwise(op) || is_binary_elementwise(op); }
+inline bool is_row_reduce(OpKind op) { return op == OpKind::RowSum || op == OpKind::RowMax; }
 inline bool is_compute(OpKind op) { return op != OpKind::Input && op != OpKind::Constant; }
 int op_arity(OpKind op);  // -1 for FusedElementwise
 
@@ -176,6 +183,7 @@ struct GraphStats {
     std::size_t fused_nodes = 0;
     std::size_t elementwise_ops = 0;
     std::size_t matmuls = 0;
+    std::size_t reductions = 0;
     std::map<std::string, std::size_t> op_counts;
 };
 

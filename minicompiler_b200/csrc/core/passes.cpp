@@ -121,6 +121,23 @@ void evaluate_node_on_host(const Node& node, const std::vector<const float*>& op
         }
         return;
     }
+    if (is_row_reduce(node.op)) {
+        // One result per row of the operand's last dimension; sums accumulate in double and round once.
+        const std::int64_t width = operand_shapes[0].back();
+        for (std::size_t r = 0; r < count; ++r) {
+            const float* row = operands[0] + static_cast<std::int64_t>(r) * width;
+            if (node.op == OpKind::RowSum) {
+                double acc = 0.0;
+                for (std::int64_t c = 0; c < width; ++c) acc += static_cast<double>(row[c]);
+                out[r] = static_cast<float>(acc);
+            } else {
+                float best = row[0];
+                for (std::int64_t c = 1; c < width; ++c) best = row[c] > best ? row[c] : best;
+                out[r] = best;
+            }
+        }
+        return;
+    }
     std::vector<std::vector<std::int64_t>> strides;
     for (const Shape& s : operand_shapes) strides.push_back(broadcast_strides(s, oshape));
     if (node.op == OpKind::FusedElementwise) {

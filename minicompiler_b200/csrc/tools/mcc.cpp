@@ -180,6 +180,14 @@ int main(int argc, char** argv) {
     if (opt.emit_cuda) {
         for (std::size_t i = 0; i < graph.num_nodes(); ++i) {
             const Node& n = graph.node(static_cast<NodeId>(i));
+            if (is_row_reduce(n.op)) {  // the node on its own: identity prologue
+                FusedProgram identity;
+                identity.instrs.push_back(FusedInstr::load(0));
+                const Shape& in_shape = graph.node(n.inputs[0]).type.shape;
+                std::cout << "// node %" << i << " '" << n.name << "' : " << to_string(n.type) << "\n"
+                          << cuda::generate_row_reduce_kernel(n.op, identity, {in_shape}, in_shape).source << "\n";
+                continue;
+            }
             if (!is_elementwise(n.op) && n.op != OpKind::FusedElementwise) continue;
             std::vector<Shape> shapes;
             for (NodeId in : n.inputs) shapes.push_back(graph.node(in).type.shape);

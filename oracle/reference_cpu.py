@@ -79,6 +79,16 @@ def normal_values(count: int, seed: int, mean: float = 0.0, std: float = 1.0) ->
 
 UNARY = ("neg", "exp", "log", "sqrt", "relu", "sigmoid", "tanh")
 BINARY = ("add", "sub", "mul", "div")
+# Row reductions: an extension of this build with no counterpart in the reference (its README.md:561-562 lists
+# reductions as future work), so their parity is unpinned. Definition: the last dimension collapses to extent 1;
+# row_sum is the double-precision sum rounded to float32 once, row_max the largest element (no NaN expected).
+REDUCE = ("row_sum", "row_max")
+
+
+def _reduce(op: str, x: np.ndarray) -> np.ndarray:
+    if op == "row_sum":
+        return np.sum(x.astype(np.float64), axis=-1, keepdims=True).astype(np.float32)
+    return np.max(x, axis=-1, keepdims=True)
 
 
 @dataclass
@@ -176,6 +186,10 @@ def parse_mcg(text: str, dims: Optional[Dict[str, int]] = None) -> McgGraph:
                 shape = ops[0].shape
             elif op in BINARY:
                 shape = _broadcast(ops[0].shape, ops[1].shape)
+            elif op in REDUCE:
+                if len(ops[0].shape) < 1:
+                    raise ValueError(f"{name}: {op} expects an operand of rank 1 or more")
+                shape = tuple(ops[0].shape[:-1]) + (1,)
             elif op == "matmul":
                 if len(ops[0].shape) != 2 or len(ops[1].shape) != 2 or ops[0].shape[1] != ops[1].shape[0]:
                     raise ValueError(f"{name}: bad matmul shapes {ops[0].shape} x {ops[1].shape}")
@@ -258,6 +272,8 @@ def evaluate_f32(graph: McgGraph, inputs: Sequence[np.ndarray]) -> List[np.ndarr
             elif n.op in BINARY:
                 r = _binary(n.op, values[n.operands[0]], values[n.operands[1]])
                 values[n.name] = np.broadcast_to(r, n.shape).astype(np.float32, copy=False)
+            elif n.op in REDUCE:
+                values[n.name] = _reduce(n.op, values[n.operands[0]])
             else:
                 values[n.name] = np.matmul(values[n.operands[0]], values[n.operands[1]]).astype(np.float32, copy=False)
     return [np.ascontiguousarray(values[o]).reshape(-1) for o in graph.outputs]
@@ -292,6 +308,9 @@ def evaluate_f64(graph: McgGraph, inputs: Sequence[np.ndarray]) -> List[np.ndarr
                 continue
             if n.op == "const":
                 values[n.name] = n.value
+                continue
+            if n.op in REDUCE:
+                values[n.name] = _reduce(n.op, values[n.operands[0]])
                 continue
             ops = [values[o].astype(np.float64) for o in n.operands]
             if n.op in UNARY:

@@ -457,3 +457,60 @@ def test_run_on_pinned_host_memory_equals_run_with_copies(mc, oracle):
     with mc.CompiledGraph(text=text, passes="none") as exe:
         exe.run_ptrs([p.data_ptr() for p in pins], [out.data_ptr()])
     assert np.array_equal(out.numpy(), want)
+
+
+# ------------------------------------------------ row reductions (extension)
+
+
+@pytest.mark.parametrize("shape", ["[5, 1]", "[7, 33]", "[64, 1000]", "[3, 1024]", "[2, 5, 5000]", "[300, 7]", "[4097]"])
+def test_row_reductions_match_the_oracle(mc, oracle, shape):
+    """row_max is exact; row_sum (FP32 partial sums in a fixed order) stays within n * 2^-24 * sum|x| of the
+    double-precision sum that defines the op, and two runs give the same bits."""
+    text = f"input x : f32{shape}\ns = row_sum x\nm = row_max x\noutput s, m"
+    g, ins = oracle_inputs(oracle, text, seed=5, lo=-3.0, hi=3.0)
+    width = int(shape.strip("[]").split(",")[-1])
+    want_s, want_m = oracle.evaluate_f64(g, ins)
+    with mc.CompiledGraph(text=text, passes="none") as exe:
+        got_s, got_m = exe.run(ins)
+        again_s, _ = exe.run(ins)
+    assert np.array_equal(got_m, want_m)
+    assert np.array_equal(got_s, again_s)
+    abs_sum = np.abs(ins[0].astype(np.float64)).reshape(-1, width).sum(axis=1)
+    err = np.abs(got_s.astype(np.float64) - want_s.astype(np.float64))
+    assert np.all(err <= width * U32 * abs_sum + U32 * np.abs(want_s)), f"{shape}: worst {float(np.max(err / abs_sum)):.2e} of sum|x|"
+
+
+def test_row_reduction_with_an_absorbed_broadcasting_producer(mc, oracle):
+    text = ("input x : f32[6, 3, 700]\ninput b : f32[3, 1]\ninput r : f32[700]\nt = mul x, b\nu = add t, r\nv = exp u\n"
+            "s = row_sum v\nm = row_max v\noutput s, m")
+    g, ins = oracle_inputs(oracle, text, seed=9, lo=-1.0, hi=1.0)
+    want_s, want_m = oracle.evaluate_f64(g, ins)
+    with mc.CompiledGraph(text=text) as exe:
+        got_s, got_m = exe.run(ins)
+        launches = exe.kernel_launches
+    assert launches == 3  # exp(...) has two readers and is written once; both reductions read it
+    ok, msg = all_close(got_m, want_m, 1e-6, 1.2e-7)
+    assert ok, msg
+    ok, msg = all_close(got_s, want_s, 1e-5, 0.0)
+    assert ok, msg
+    single = "input x : f32[6, 3, 700]\ninput b : f32[3, 1]\nt = mul x, b\nq = mul t, t\ns = row_sum q\noutput s"
+    g, ins = oracle_inputs(oracle, single, seed=9, lo=-1.0, hi=1.0)
+    with mc.CompiledGraph(text=single) as exe:
+        got = exe.run(ins)[0]
+        assert exe.kernel_launches == 1  # the whole producer chain is evaluated inside the reduction
+    ok, msg = all_close(got, oracle.evaluate_f64(g, ins)[0], 1e-5, 0.0)
+    assert ok, msg
+
+
+def test_softmax_and_layernorm_graphs(mc, oracle):
+    for name, dims in [("x1_softmax", "M=128,N=1000"), ("x1_softmax", "M=64,N=4096"), ("x2_layernorm", "M=96,N=4096")]:
+        path = mc.graph_path(name)
+        g, _ = oracle_inputs(oracle, path=path, dims=dims)
+        x = oracle.normal_values(int(np.prod(g.node(g.inputs[0]).shape)), 7)
+        want = oracle.evaluate_f64(g, [x])[0]
+        with mc.CompiledGraph(path, dims=dims) as exe:
+            got = exe.run([x])[0]
+        assert norm_scaled_error(got, want) <= 1e-5, f"{name} {dims}: {norm_scaled_error(got, want):.2e}"
+        if name == "x1_softmax":
+            width = int(dims.split("N=")[1])
+            assert np.allclose(got.reshape(-1, width).sum(axis=1), 1.0, atol=1e-5)

@@ -455,3 +455,56 @@ def test_mcc_emit_cuda_and_listings_need_no_gpu(mc):
     assert "dne" in out.stdout and "fold" in out.stdout and "fuse" in out.stdout
     out = subprocess.run([str(mcc), mc.graph_path("c2_gelu_chain"), "--backend", "cpu", "--run"], capture_output=True, text=True)
     assert out.returncode != 0 and "no CPU execution path" in out.stderr
+
+
+# ------------------------------------------------ row reductions (extension)
+
+
+def test_row_reductions_parse_print_and_type_check(mc):
+    text = "input x : f32[4, 3, 8]\nm = row_max x\ns = row_sum x\nd = sub x, m\noutput d, s"
+    g = mc.HostGraph(text=text, passes="none")
+    printed = g.print()
+    assert "m = row_max %0 : f32[4,3,1]" in printed and "s = row_sum %0 : f32[4,3,1]" in printed
+    assert "d = sub %0, %1 : f32[4,3,8]" in printed  # the reduced value broadcasts back against its operand
+    with pytest.raises(mc.McError, match="row_sum expects an operand of rank 1 or more"):
+        mc.HostGraph(text="const c : f32[] = 1\ns = row_sum c\noutput s")
+    with pytest.raises(mc.McError, match="row_max expects 1 operand"):
+        mc.HostGraph(text="input x : f32[4]\ns = row_max x, x\noutput s")
+
+
+def test_constant_row_reductions_fold_to_known_answers(mc):
+    text = ("const c : f32[2, 3] = [1, 2, 3, -4, 5.5, 0.25]\nconst big : f32[4] = [16777216, 1, 1, 1]\n"
+            "s = row_sum c\nm = row_max c\nb = row_sum big\ninput x : f32[2, 3]\ny = add x, s\nz = mul y, m\nw = add z, b\noutput w")
+    g = mc.HostGraph(text=text, passes="fold")
+    assert g.constant("s").tolist() == [6.0, 1.75]
+    assert g.constant("m").tolist() == [3.0, 5.5]
+    # accumulated in double and rounded once: 16777219 rounds to 16777220 (a float32 running sum would stay at 16777216)
+    assert g.constant("b").tolist() == [16777220.0]
+
+
+def test_row_reduction_lowering_absorbs_a_producer_read_by_nothing_else(mc):
+    g = mc.HostGraph(mc.graph_path("x2_layernorm"), dims="M=64,N=4096")
+    plan = g.launch_plan({})
+    assert "row_sum total rows of 4096 prologue_ops=0" in plan
+    assert "row_sum ss rows of 4096 prologue_ops=1" in plan and "elementwise sq" not in plan  # (x-mean)^2 is never written
+    assert "elementwise c " in plan  # x-mean has a second reader and stays a tensor
+    assert "launches=6 " in plan
+    soft = mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=4096").launch_plan({})
+    assert soft.count("row_") == 2 and "launches=4 " in soft
+    # an output, or a value with two readers, is not absorbed
+    kept = mc.HostGraph(text="input x : f32[8, 64]\ne = exp x\ns = row_sum e\noutput s, e").launch_plan({})
+    assert "prologue_ops=0" in kept and "elementwise e" in kept
+
+
+def test_row_reduction_kernel_text_and_compilation(mc):
+    wide = mc.HostGraph(text="input x : f32[8, 3, 2048]\ninput b : f32[3, 1]\nt = mul x, b\ns = row_max t\noutput s")
+    src = wide.emit_cuda()
+    assert "mc_row_reduce(float* __restrict__ out, const float* __restrict__ in0, unsigned rows)" in src
+    assert "fmaxf(a, b)" in src and "__uint_as_float(0xff800000u)" in src and "256 threads per row" in src
+    assert "__shfl_xor_sync(0xffffffffu, total, offset)" in src and "warp_total[8]" in src
+    narrow = mc.HostGraph(text="input x : f32[100, 33]\ns = row_sum x\noutput s").emit_cuda()
+    assert "32 threads per row" in narrow and "return a + b;" in narrow and "__syncthreads" not in narrow
+    for g in (wide, mc.HostGraph(text="input x : f32[100, 33]\ns = row_sum x\noutput s"),
+              mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=256"),
+              mc.HostGraph(mc.graph_path("x2_layernorm"), dims="M=64,N=4096")):
+        g.check_kernels({})

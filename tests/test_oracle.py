@@ -128,3 +128,15 @@ def test_normal_generator_is_seeded_and_standard(oracle):
     a = oracle.normal_values(200000, 7)
     assert np.array_equal(a, oracle.normal_values(200000, 7)) and not np.array_equal(a, oracle.normal_values(200000, 8))
     assert abs(float(a.mean())) < 0.01 and abs(float(a.std()) - 1.0) < 0.01
+
+
+def test_row_reductions_of_the_oracle_known_answers(oracle):
+    """The extension ops as the oracle defines them: last dimension to extent 1, sums in double rounded once."""
+    g = oracle.parse_mcg("input x : f32[2, 4]\ns = row_sum x\nm = row_max x\nd = sub x, m\noutput s, m, d")
+    x = np.array([[16777216, 1, 1, 1], [-1, -2, -0.5, -8]], dtype=np.float32)
+    s, m, d = oracle.evaluate_f32(g, [x])
+    assert s.tolist() == [16777220.0, -11.5] and m.tolist() == [16777216.0, -0.5]
+    assert d.reshape(2, 4)[1].tolist() == [-0.5, -1.5, 0.0, -7.5]
+    s64, m64, _ = oracle.evaluate_f64(g, [x])
+    assert np.array_equal(s64, s) and np.array_equal(m64, m)
+    assert g.node("s").shape == (2, 1)
