@@ -59,6 +59,10 @@ Result<ShardPlan> plan_batch_shard(std::string_view text, const std::map<std::st
             return Error{"matmul '" + n.name + "' has a right-hand side that carries dim '" + batch_dim +
                          "': its rows would need an exchange between devices"};
         }
+        if (is_row_reduce(n.op) && carries[static_cast<std::size_t>(n.inputs[0])] && whole.node(n.inputs[0]).type.rank() < 2) {
+            return Error{std::string(op_name(n.op)) + " '" + n.name + "' reduces over dim '" + batch_dim +
+                         "': its partial results would need an exchange between devices"};
+        }
         // A batch-carrying operand broadcast against a same-extent non-batch operand would silently change meaning.
         if (is_binary_elementwise(n.op) && carries[i]) {
             for (NodeId in : n.inputs) {

@@ -508,3 +508,13 @@ def test_row_reduction_kernel_text_and_compilation(mc):
               mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=256"),
               mc.HostGraph(mc.graph_path("x2_layernorm"), dims="M=64,N=4096")):
         g.check_kernels({})
+
+
+def test_sharding_rules_for_row_reductions(mc, tmp_path):
+    assert mc.shard_dims(mc.graph_path("x1_softmax"), {"M": 64, "N": 128}, "M", 1, 2) == ("M=32,N=128", 32, 32)
+    with pytest.raises(mc.McError, match="carries dim 'N' other than as its leading extent"):
+        mc.shard_dims(mc.graph_path("x1_softmax"), {"M": 64, "N": 128}, "N", 1, 2)
+    flat = tmp_path / "flat.mcg"
+    flat.write_text("dim B = 64\ninput x : f32[B]\ns = row_sum x\noutput s\n")
+    with pytest.raises(mc.McError, match="row_sum 's' reduces over dim 'B'"):
+        mc.shard_dims(str(flat), {}, "B", 0, 2)
