@@ -145,6 +145,108 @@ bool classify_epilogue_operand(const Shape& operand, const Shape& out, EpilogueO
     return false;
 }
 
+// `user` reads value `value`, which `producer` computes: returns the program that evaluates the producer's
+// instructions in place of those loads, over the user's other inputs followed by the producer's inputs it did not
+// already read. Per element it performs the same operations in the same order as the two programs did.
+void inline_producer(Step* user, NodeId value, const Step& producer) {
+    std::vector<NodeId> inputs;
+    for (NodeId in : user->inputs) {
+        if (in != value && std::find(inputs.begin(), inputs.end(), in) == inputs.end()) inputs.push_back(in);
+    }
+    for (NodeId in : producer.inputs) {
+        if (std::find(inputs.begin(), inputs.end(), in) == inputs.end()) inputs.push_back(in);
+    }
+    auto slot_of = [&](NodeId in) {
+        return static_cast<std::int32_t>(std::find(inputs.begin(), inputs.end(), in) - inputs.begin());
+    };
+    FusedProgram merged;
+    merged.source_nodes = producer.program.source_nodes;
+    merged.source_nodes.insert(merged.source_nodes.end(), user->program.source_nodes.begin(), user->program.source_nodes.end());
+    std::vector<std::int32_t> reg_of_producer(producer.program.instrs.size());
+    for (std::size_t r = 0; r < producer.program.instrs.size(); ++r) {
+        FusedInstr ins = producer.program.instrs[r];
+        if (ins.kind == FusedInstr::Kind::Load) {
+            ins.a = slot_of(producer.inputs[static_cast<std::size_t>(ins.a)]);
+        } else if (ins.kind != FusedInstr::Kind::Immediate) {
+            ins.a = reg_of_producer[static_cast<std::size_t>(ins.a)];
+            if (ins.kind == FusedInstr::Kind::Binary) ins.b = reg_of_producer[static_cast<std::size_t>(ins.b)];
+        }
+        reg_of_producer[r] = static_cast<std::int32_t>(merged.instrs.size());
+        merged.instrs.push_back(ins);
+    }
+    const std::int32_t produced = reg_of_producer.back();
+    std::vector<std::int32_t> reg_of_user(user->program.instrs.size());
+    for (std::size_t r = 0; r < user->program.instrs.size(); ++r) {
+        FusedInstr ins = user->program.instrs[r];
+        if (ins.kind == FusedInstr::Kind::Load) {
+            const NodeId in = user->inputs[static_cast<std::size_t>(ins.a)];
+            if (in == value) {
+                reg_of_user[r] = produced;
+                continue;
+            }
+            ins.a = slot_of(in);
+        } else if (ins.kind != FusedInstr::Kind::Immediate) {
+            ins.a = reg_of_user[static_cast<std::size_t>(ins.a)];
+            if (ins.kind == FusedInstr::Kind::Binary) ins.b = reg_of_user[static_cast<std::size_t>(ins.b)];
+        }
+        reg_of_user[r] = static_cast<std::int32_t>(merged.instrs.size());
+        merged.instrs.push_back(ins);
+    }
+    if (reg_of_user.back() != static_cast<std::int32_t>(merged.instrs.size()) - 1) {
+        // The user's result is the produced value itself: the result must be the last instruction.
+        merged.instrs.push_back(merged.instrs[static_cast<std::size_t>(reg_of_user.back())]);
+    }
+    user->program = std::move(merged);
+    user->inputs = std::move(inputs);
+}
+
+// The shape a step evaluates its program over.
+const Shape& evaluation_shape(const Graph& graph, const Step& s) {
+    return s.kind == Step::Kind::Reduce ? s.reduce_shape : graph.node(s.result).type.shape;
+}
+
+// An elementwise value that a row reduction reads, together with other elementwise or reduction steps of the same
+// shape, is recomputed by each of them instead of being written once and read back: the readers already stream
+// tensors of that size, so this removes one write and one read pass (softmax: exp(x - max); LayerNorm: x - mean).
+// Only cheap producers qualify, and only when every reader can take them.
+void rematerialize_for_reductions(const Graph& graph, std::vector<Step>* steps) {
+    constexpr std::size_t kMaxProducerOps = 16;
+    constexpr std::size_t kMaxInputs = 8;
+    for (std::size_t pi = 0; pi < steps->size();) {
+        const Step& producer = (*steps)[pi];
+        const NodeId value = producer.result;
+        bool candidate = producer.kind == Step::Kind::Elementwise && !graph.is_output(value) &&
+                         producer.program.num_ops() <= kMaxProducerOps;
+        std::vector<std::size_t> readers;
+        bool feeds_reduction = false;
+        for (std::size_t ui = 0; candidate && ui < steps->size(); ++ui) {
+            const Step& user = (*steps)[ui];
+            if (user.kind == Step::Kind::Matmul) {
+                const bool reads = user.lhs == value || user.rhs == value ||
+                                   std::find(user.inputs.begin(), user.inputs.end(), value) != user.inputs.end();
+                if (reads) candidate = false;
+                continue;
+            }
+            if (std::find(user.inputs.begin(), user.inputs.end(), value) == user.inputs.end()) continue;
+            if (evaluation_shape(graph, user) != graph.node(value).type.shape) candidate = false;
+            std::size_t merged_inputs = producer.inputs.size();
+            for (NodeId in : user.inputs) {
+                if (in != value && std::find(producer.inputs.begin(), producer.inputs.end(), in) == producer.inputs.end()) ++merged_inputs;
+            }
+            if (merged_inputs > kMaxInputs) candidate = false;
+            feeds_reduction = feeds_reduction || user.kind == Step::Kind::Reduce;
+            readers.push_back(ui);
+        }
+        if (!candidate || !feeds_reduction || readers.size() < 2) {
+            ++pi;
+            continue;
+        }
+        const Step copy = producer;
+        for (std::size_t ui : readers) inline_producer(&(*steps)[ui], value, copy);
+        steps->erase(steps->begin() + static_cast<std::ptrdiff_t>(pi));
+    }
+}
+
 }  // namespace
 
 Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options, int sm_count) {
@@ -279,7 +381,10 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
             s.inputs = n.inputs;
             out.steps.push_back(std::move(s));
         }
-        step_of[i] = static_cast<std::int32_t>(out.steps.size()) - 1;
+    }
+    if (options.rematerialize) rematerialize_for_reductions(graph, &out.steps);
+    for (std::size_t i = 0; i < out.steps.size(); ++i) {
+        step_of[static_cast<std::size_t>(out.steps[i].result)] = static_cast<std::int32_t>(i);
     }
 
     // What form each value is read in.

@@ -83,6 +83,7 @@ struct CudaOptions {
     // 256-thread blocks with four 128-bit loads in flight per thread stream faster than eight (6.1 vs
     // 5.5 TB/s on the 512 MiB GELU pass): more outstanding requests than that only queue up in front of HBM.
     int eltwise_blocks_per_sm = 4;
+    bool rematerialize = true;  // recompute cheap elementwise values read by a row reduction in each reader
 };
 
 enum class Arith : int { F32 = 0, Tf32 = 1, Bf16 = 2, F16 = 3 };  // same numbering as MCD_GEMM_*

@@ -115,6 +115,8 @@ Status parse_options(const char* text, cuda::CudaOptions* options) {
                 options->streaming_hints = number != 0;
             } else if (key == "gemm_variant") {
                 options->gemm_variant = static_cast<int>(number);
+            } else if (key == "rematerialize") {
+                options->rematerialize = number != 0;
             } else if (key == "host_io") {
                 options->host_io = static_cast<int>(number);
             } else if (key == "graph") {
@@ -125,7 +127,7 @@ Status parse_options(const char* text, cuda::CudaOptions* options) {
                 options->eltwise_blocks_per_sm = static_cast<int>(number);
             } else {
                 return Error{"unknown option '" + key +
-                             "' (device, matmul, vectorize, fuse_epilogue, b_layout, unroll, streaming, gemm_variant, fmad, blocks_per_sm, graph, host_io)"};
+                             "' (device, matmul, vectorize, fuse_epilogue, b_layout, unroll, streaming, gemm_variant, fmad, blocks_per_sm, graph, host_io, rematerialize)"};
             }
         }
     }

@@ -485,14 +485,15 @@ def test_row_reduction_with_an_absorbed_broadcasting_producer(mc, oracle):
             "s = row_sum v\nm = row_max v\noutput s, m")
     g, ins = oracle_inputs(oracle, text, seed=9, lo=-1.0, hi=1.0)
     want_s, want_m = oracle.evaluate_f64(g, ins)
-    with mc.CompiledGraph(text=text) as exe:
-        got_s, got_m = exe.run(ins)
-        launches = exe.kernel_launches
-    assert launches == 3  # exp(...) has two readers and is written once; both reductions read it
-    ok, msg = all_close(got_m, want_m, 1e-6, 1.2e-7)
-    assert ok, msg
-    ok, msg = all_close(got_s, want_s, 1e-5, 0.0)
-    assert ok, msg
+    for options, launches in [({}, 2), ({"rematerialize": 0}, 3)]:
+        # exp(...) has two readers: by default each reduction recomputes it, otherwise it is written once
+        with mc.CompiledGraph(text=text, options=options) as exe:
+            got_s, got_m = exe.run(ins)
+            assert exe.kernel_launches == launches
+        ok, msg = all_close(got_m, want_m, 1e-6, 1.2e-7)
+        assert ok, msg
+        ok, msg = all_close(got_s, want_s, 1e-5, 0.0)
+        assert ok, msg
     single = "input x : f32[6, 3, 700]\ninput b : f32[3, 1]\nt = mul x, b\nq = mul t, t\ns = row_sum q\noutput s"
     g, ins = oracle_inputs(oracle, single, seed=9, lo=-1.0, hi=1.0)
     with mc.CompiledGraph(text=single) as exe:
@@ -510,6 +511,9 @@ def test_softmax_and_layernorm_graphs(mc, oracle):
         want = oracle.evaluate_f64(g, [x])[0]
         with mc.CompiledGraph(path, dims=dims) as exe:
             got = exe.run([x])[0]
+        with mc.CompiledGraph(path, dims=dims, options={"rematerialize": 0}) as exe:
+            written = exe.run([x])[0]
+        assert np.array_equal(got, written)  # recomputing a value performs the same operations per element
         assert norm_scaled_error(got, want) <= 1e-5, f"{name} {dims}: {norm_scaled_error(got, want):.2e}"
         if name == "x1_softmax":
             width = int(dims.split("N=")[1])

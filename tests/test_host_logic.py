@@ -482,18 +482,25 @@ def test_constant_row_reductions_fold_to_known_answers(mc):
     assert g.constant("b").tolist() == [16777220.0]
 
 
-def test_row_reduction_lowering_absorbs_a_producer_read_by_nothing_else(mc):
+def test_row_reduction_lowering_absorbs_and_rematerializes_producers(mc):
     g = mc.HostGraph(mc.graph_path("x2_layernorm"), dims="M=64,N=4096")
+    plain = g.launch_plan({"rematerialize": 0})
+    assert "row_sum total rows of 4096 prologue_ops=0" in plain
+    # (x-mean)^2 is read by the reduction only: evaluated inside it, never written
+    assert "row_sum ss rows of 4096 prologue_ops=1" in plain and "elementwise sq" not in plain
+    assert "elementwise c " in plain and "launches=6 " in plain  # x-mean has a second reader and stays a tensor
+    # by default a cheap value read by a reduction and by other steps is recomputed in each of them
     plan = g.launch_plan({})
-    assert "row_sum total rows of 4096 prologue_ops=0" in plan
-    assert "row_sum ss rows of 4096 prologue_ops=1" in plan and "elementwise sq" not in plan  # (x-mean)^2 is never written
-    assert "elementwise c " in plan  # x-mean has a second reader and stays a tensor
-    assert "launches=6 " in plan
-    soft = mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=4096").launch_plan({})
-    assert soft.count("row_") == 2 and "launches=4 " in soft
-    # an output, or a value with two readers, is not absorbed
+    assert "elementwise c " not in plan and "row_sum ss rows of 4096 prologue_ops=2" in plan
+    assert "elementwise y ops=4" in plan and "launches=5 " in plan
+    soft = mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=4096")
+    assert "launches=4 " in soft.launch_plan({"rematerialize": 0})
+    assert "row_sum s rows of 4096 prologue_ops=2" in soft.launch_plan({}) and "launches=3 " in soft.launch_plan({})
+    # an output is written in any case; graphs without reductions are lowered as before
     kept = mc.HostGraph(text="input x : f32[8, 64]\ne = exp x\ns = row_sum e\noutput s, e").launch_plan({})
     assert "prologue_ops=0" in kept and "elementwise e" in kept
+    chain = mc.HostGraph(str(GOLDEN / "graphs" / "ref_gelu_chain.mcg"), dims="M=64,N=64", passes="none")
+    assert chain.launch_plan({}) == chain.launch_plan({"rematerialize": 0})
 
 
 def test_row_reduction_kernel_text_and_compilation(mc):
