@@ -6,7 +6,7 @@ One "step" is one execution of a compiled graph (`mc_enqueue`) on inputs already
 The default workload is the headline memory-bound config: the tanh-GELU chain on f32[8192,8192]
 (one fused kernel; 536,870,912 algorithmic bytes per step), reported as fused-eltwise HBM GB/s.
 Other workloads (`--workload`): c1, c3_fp32, c3_tf32, c4_bf16, c4_f16, c4_tf32, c4_fp32, c5_f16, c5_bf16
-report graph TFLOP/s. With N > 1 (launched by torchrun, one rank per GPU) c2/c4 run one replica per
+report graph TFLOP/s; x1_softmax and x2_layernorm (extension graphs) report GB/s of read-x-plus-write-y bytes. With N > 1 (launched by torchrun, one rank per GPU) c2/c4 run one replica per
 GPU on rank-specific data (weak scaling) and c5/c3/c1 shard their batch dim over the ranks.
 
 Rank 0 prints ONE JSON line. `value` is device-timed with CUDA events on the launching stream,
@@ -46,6 +46,9 @@ WORKLOADS = {
     "c4_fp32": ("c4_matmul", {"M": 4096, "N": 4096, "K": 4096}, "auto", None, "flops", "uniform"),
     "c5_f16": ("c5_mlp_stack", {"B": 65536, "D": 2048}, "tensor_core_f16", "B", "flops", "normal"),
     "c5_bf16": ("c5_mlp_stack", {"B": 65536, "D": 2048}, "tensor_core_bf16", "B", "flops", "normal"),
+    # Extension graphs built from the row reductions; bytes = read x + write y, what a single fused kernel would move.
+    "x1_softmax": ("x1_softmax", {"M": 8192, "N": 8192}, "auto", "M", "bytes", "normal"),
+    "x2_layernorm": ("x2_layernorm", {"M": 16384, "N": 4096}, "auto", "M", "bytes", "normal"),
 }
 # The rest of the C4 sweep: squares, skinny-M and tall-K shapes, per 16-bit format.
 for _fmt in ("bf16", "f16"):
@@ -152,7 +155,7 @@ def cpu_sample(oracle, path, dims, batch_dim, kind, dist, rows_cap):
     threads = cpu_baseline.max_threads()
     plan = cpu_baseline.CpuPlan(g, threads)
     ins = make_inputs(oracle, g, dist, 1)
-    return plan, ins, algorithmic_work(oracle, g, kind), threads, f"{rows} of {rows_full} rows of '{lead}'"
+    return plan, ins, algorithmic_work(oracle, g, kind), plan.threads, f"{rows} of {rows_full} rows of '{lead}'"
 
 
 def cpu_sample_rate(oracle, path, dims, batch_dim, kind, dist, seconds_target=10.0):
@@ -167,7 +170,7 @@ def cpu_sample_rate(oracle, path, dims, batch_dim, kind, dist, seconds_target=10
         if dt > seconds_target or reps >= 200:
             break
     rate = work * reps / dt / (1e9 if kind == "bytes" else 1e12)
-    return rate, threads, f"{what}, {reps} runs in {dt:.1f} s, C port of the reference CPU kernels with {threads} OpenMP threads"
+    return rate, threads, f"{what}, {reps} runs in {dt:.1f} s, {plan.how}"
 
 
 def run_reference_arm(args):

@@ -84,6 +84,12 @@ class CpuPlan:
 
     def __init__(self, graph: orc.McgGraph, threads: int = 1):
         self.g, self.threads = graph, max(1, threads)
+        # Graphs with row reductions (an extension without a C port) run through the numpy restatement, one thread.
+        self.numpy_only = any(n.op in orc.REDUCE for n in graph.nodes)
+        if self.numpy_only:
+            self.threads = 1
+        self.how = ("numpy restatement of the CPU path, 1 thread" if self.numpy_only
+                    else f"C port of the reference CPU kernels with {self.threads} OpenMP threads")
         self.users: Dict[str, List[str]] = {n.name: [] for n in graph.nodes}
         for n in graph.nodes:
             for o in n.operands:
@@ -100,7 +106,7 @@ class CpuPlan:
                 self.values[n.name] = np.ascontiguousarray(orc.evaluate_f32(sub, [])[0].reshape(n.shape))
                 const.add(n.name)
         self.const = const
-        self.segments = self._segment()
+        self.segments = [] if self.numpy_only else self._segment()
 
     def _closure(self, name: str) -> List[str]:
         need, order = set(), []
@@ -143,6 +149,8 @@ class CpuPlan:
         return segs
 
     def run(self, inputs: Sequence[np.ndarray]) -> List[np.ndarray]:
+        if self.numpy_only:
+            return orc.evaluate_f32(self.g, inputs)
         L = _load()
         vals = dict(self.values)
         for name, a in zip(self.g.inputs, inputs):
