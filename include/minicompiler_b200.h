@@ -119,6 +119,10 @@ MC_EXPORT int mcb_graph_num_nodes(const void* graph);
 MC_EXPORT long long mcb_graph_constant(const void* graph, const char* name, float* out, long long capacity);
 /* NVRTC-compiles every kernel the launch plan would generate, for sm_100a, without loading it. 0 ok. */
 MC_EXPORT int mcb_graph_check_kernels(const void* graph, const char* options, int sm_count);
+/* The CUDA text the launch plan generates, step by step (elementwise, reduction and row-fused kernels, matmul
+ * epilogues); same return convention as mcb_graph_launch_plan. Unlike `--emit-cuda`, which follows the
+ * reference and prints one kernel per graph node (tools/mcc.cpp:200-210), this is what actually runs. */
+MC_EXPORT int mcb_graph_plan_sources(const void* graph, const char* options, int sm_count, char* out, int size);
 
 MC_EXPORT void mcb_uniform_values(float* out, long long count, unsigned long long seed, float lo, float hi);
 MC_EXPORT int mcb_split_k_splits(int m, int n, int k, int sm_count, int blocks_per_sm);

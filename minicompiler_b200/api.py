@@ -73,6 +73,7 @@ def lib() -> C.CDLL:
         "mcb_graph_fusion_groups": (i32, [vp, cp, i32]),
         "mcb_graph_emit_cuda": (i32, [vp, cp, cp, i32]),
         "mcb_graph_launch_plan": (i32, [vp, cp, i32, cp, i32]),
+        "mcb_graph_plan_sources": (i32, [vp, cp, i32, cp, i32]),
         "mcb_graph_num_nodes": (i32, [vp]),
         "mcb_graph_constant": (i64, [vp, cp, C.POINTER(C.c_float), i64]),
         "mcb_graph_check_kernels": (i32, [vp, cp, i32]),
@@ -330,6 +331,10 @@ class HostGraph:
 
     def launch_plan(self, options=None, sm_count: int = 148) -> str:
         return _read_string(lib().mcb_graph_launch_plan, self._g, _enc(_opts_str(options)), sm_count)
+
+    def plan_sources(self, options=None, sm_count: int = 148) -> str:
+        """The CUDA text the launch plan generates, step by step (no GPU needed)."""
+        return _read_string(lib().mcb_graph_plan_sources, self._g, _enc(_opts_str(options)), sm_count)
 
     def constant(self, name: str) -> np.ndarray:
         n = lib().mcb_graph_constant(self._g, name.encode(), None, 0)

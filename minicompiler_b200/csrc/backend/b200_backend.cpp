@@ -480,6 +480,8 @@ private:
             const Step& step = lowered_.steps[i];
             if (step.kind == Step::Kind::Elementwise) {
                 MC_TRY(add_elementwise(step));
+            } else if (step.kind == Step::Kind::RowFused) {
+                MC_TRY(add_row_fused(step));
             } else if (step.kind == Step::Kind::Reduce) {
                 MC_TRY(add_reduce(step));
             } else {
@@ -600,6 +602,38 @@ private:
         launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(wanted, resident)));
         launch->pointers.push_back(address(step.result, kRepF32));
         launch->advances.push_back(0);
+        for (NodeId in : step.inputs) {
+            launch->pointers.push_back(address(in, kRepF32));
+            launch->advances.push_back(0);
+        }
+        for (void*& p : launch->pointers) launch->params.push_back(&p);
+        launch->params.push_back(&launch->count);
+        launches_.push_back(std::move(launch));
+        return Status();
+    }
+
+    // A run of steps on rows of one shape as one kernel, a block per row.
+    Status add_row_fused(const Step& step) {
+        const std::string source = generate_row_fused_kernel(step.row_parts, step.row_externals,
+                                                             static_cast<int>(step.row_outputs.size()), step.reduce_shape.back());
+        auto launch = std::make_unique<Launch>();
+        launch->kind = Launch::Kind::Elementwise;
+        double ms = 0.0;
+        if (mcd_jit_kernel(options_.device, source.c_str(), kRowFusedKernelName, "--fmad=false", &launch->function, &ms) != 0) {
+            return Error{std::string("compiling the row kernel of '") + graph_.node(step.result).name + "' failed: " + mcd_last_error()};
+        }
+        jit_ms_ += ms;
+        sources_.push_back(source);
+        const std::size_t rows = num_elements(step.reduce_shape) / static_cast<std::size_t>(step.reduce_shape.back());
+        launch->count = static_cast<unsigned>(rows);
+        int blocks_per_sm = 0;
+        MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(kRowReduceBlock), 0, &blocks_per_sm));
+        const std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
+        launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(rows, resident)));
+        for (NodeId w : step.row_outputs) {
+            launch->pointers.push_back(address(w, kRepF32));
+            launch->advances.push_back(0);
+        }
         for (NodeId in : step.inputs) {
             launch->pointers.push_back(address(in, kRepF32));
             launch->advances.push_back(0);

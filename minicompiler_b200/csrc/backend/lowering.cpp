@@ -200,6 +200,134 @@ void inline_producer(Step* user, NodeId value, const Step& producer) {
     user->inputs = std::move(inputs);
 }
 
+// How a value of shape `operand` that lives in memory is read by a step working on rows of `rows_shape`
+// (`over_full`: the step computes one value per element, otherwise one per row).
+bool classify_row_operand(const Shape& operand, const Shape& rows_shape, bool over_full, RowOperand::Kind* kind) {
+    if (num_elements(operand) == 1) {
+        *kind = RowOperand::Kind::Scalar;
+        return true;
+    }
+    Shape reduced = rows_shape;
+    reduced.back() = 1;
+    if (operand == reduced) {
+        *kind = RowOperand::Kind::PerRow;
+        return true;
+    }
+    if (!over_full) return false;
+    if (operand == rows_shape) {
+        *kind = RowOperand::Kind::Full;
+        return true;
+    }
+    if (operand.size() <= rows_shape.size() && operand.back() == rows_shape.back() &&
+        num_elements(operand) == static_cast<std::size_t>(rows_shape.back())) {
+        *kind = RowOperand::Kind::RowVector;
+        return true;
+    }
+    return false;
+}
+
+// Runs of consecutive steps that all work on rows of one shape and contain a row reduction become one RowFused
+// step (see reduce_codegen.hpp). Steps keep their order inside the kernel, values read by nothing outside the run
+// are never written.
+void fuse_row_runs(const Graph& graph, std::vector<Step>* steps) {
+    auto reads = [](const Step& s, NodeId v) {
+        return s.lhs == v || s.rhs == v || std::find(s.inputs.begin(), s.inputs.end(), v) != s.inputs.end();
+    };
+    for (std::size_t r = 0; r < steps->size(); ++r) {
+        if ((*steps)[r].kind != Step::Kind::Reduce) continue;
+        const Shape rows_shape = (*steps)[r].reduce_shape;
+        const std::int64_t width = rows_shape.back();
+        if (width < kRowFusedMinWidth || width > kRowFusedMaxWidth) continue;
+        Shape reduced = rows_shape;
+        reduced.back() = 1;
+        // Whether a step can join, given the results of the steps already in the run (which it may read freely).
+        auto joins = [&](const Step& s, const std::vector<NodeId>& inside) {
+            bool over_full = true;
+            if (s.kind == Step::Kind::Reduce) {
+                if (s.reduce_shape != rows_shape) return false;
+            } else if (s.kind == Step::Kind::Elementwise) {
+                const Shape& shape = graph.node(s.result).type.shape;
+                if (shape != rows_shape && shape != reduced) return false;
+                over_full = shape == rows_shape;
+            } else {
+                return false;
+            }
+            for (NodeId in : s.inputs) {
+                if (std::find(inside.begin(), inside.end(), in) != inside.end()) continue;
+                RowOperand::Kind kind;
+                if (!classify_row_operand(graph.node(in).type.shape, rows_shape, over_full, &kind)) return false;
+            }
+            return true;
+        };
+        std::size_t lo = r, hi = r;
+        std::vector<NodeId> inside{(*steps)[r].result};
+        if (!joins((*steps)[r], {})) continue;
+        // Later steps may read what the run has produced; earlier steps are taken while every step already in the
+        // run stays readable (their results only replace memory operands of the same shapes).
+        while (hi + 1 < steps->size() && joins((*steps)[hi + 1], inside)) inside.push_back((*steps)[++hi].result);
+        while (lo > 0 && joins((*steps)[lo - 1], {})) inside.push_back((*steps)[--lo].result);
+        if (hi == lo) continue;
+
+        Step fused;
+        fused.kind = Step::Kind::RowFused;
+        fused.reduce_shape = rows_shape;
+        std::vector<NodeId> produced;  // value number = position
+        std::size_t full_values = 0;
+        bool ok = true;
+        for (std::size_t i = lo; i <= hi && ok; ++i) {
+            const Step& s = (*steps)[i];
+            RowPart part;
+            part.is_reduce = s.kind == Step::Kind::Reduce;
+            part.reduce_op = s.reduce_op;
+            part.program = s.program;
+            part.result = static_cast<int>(produced.size());
+            part.result_is_full = !part.is_reduce && graph.node(s.result).type.shape == rows_shape;
+            part.name = graph.node(s.result).name;
+            const bool over_full = part.is_reduce || part.result_is_full;
+            for (NodeId in : s.inputs) {
+                RowOperand operand;
+                const auto made = std::find(produced.begin(), produced.end(), in);
+                if (made != produced.end()) {
+                    operand.value = static_cast<int>(made - produced.begin());
+                    operand.kind = fused.row_parts[static_cast<std::size_t>(operand.value)].result_is_full ? RowOperand::Kind::Full
+                                                                                                           : RowOperand::Kind::PerRow;
+                    if (operand.kind == RowOperand::Kind::Full && !over_full) ok = false;
+                } else {
+                    ok = ok && classify_row_operand(graph.node(in).type.shape, rows_shape, over_full, &operand.kind);
+                    auto seen = std::find(fused.inputs.begin(), fused.inputs.end(), in);
+                    if (seen == fused.inputs.end()) {
+                        fused.inputs.push_back(in);
+                        fused.row_externals.push_back(operand.kind);
+                        if (operand.kind == RowOperand::Kind::Full) ++full_values;
+                        seen = fused.inputs.end() - 1;
+                    }
+                    operand.external = static_cast<int>(seen - fused.inputs.begin());
+                    if (fused.row_externals[static_cast<std::size_t>(operand.external)] != operand.kind) ok = false;
+                }
+                part.operands.push_back(operand);
+            }
+            if (part.result_is_full) ++full_values;
+            bool leaves = graph.is_output(s.result);
+            for (std::size_t u = 0; u < steps->size() && !leaves; ++u) {
+                if ((u < lo || u > hi) && reads((*steps)[u], s.result)) leaves = true;
+            }
+            if (leaves) {
+                part.output = static_cast<int>(fused.row_outputs.size());
+                fused.row_outputs.push_back(s.result);
+            }
+            produced.push_back(s.result);
+            fused.row_parts.push_back(std::move(part));
+        }
+        // Every full-shaped value costs width / 256 registers per thread while it is live.
+        const std::size_t per_thread = static_cast<std::size_t>((width + 255) / 256);
+        if (!ok || fused.row_outputs.empty() || full_values * per_thread > 160) continue;
+        fused.result = fused.row_outputs[0];
+        steps->erase(steps->begin() + static_cast<std::ptrdiff_t>(lo), steps->begin() + static_cast<std::ptrdiff_t>(hi) + 1);
+        steps->insert(steps->begin() + static_cast<std::ptrdiff_t>(lo), std::move(fused));
+        r = lo;
+    }
+}
+
 // The shape a step evaluates its program over.
 const Shape& evaluation_shape(const Graph& graph, const Step& s) {
     return s.kind == Step::Kind::Reduce ? s.reduce_shape : graph.node(s.result).type.shape;
@@ -221,7 +349,7 @@ void rematerialize_for_reductions(const Graph& graph, std::vector<Step>* steps) 
         bool feeds_reduction = false;
         for (std::size_t ui = 0; candidate && ui < steps->size(); ++ui) {
             const Step& user = (*steps)[ui];
-            if (user.kind == Step::Kind::Matmul) {
+            if (user.kind == Step::Kind::Matmul || user.kind == Step::Kind::RowFused) {
                 const bool reads = user.lhs == value || user.rhs == value ||
                                    std::find(user.inputs.begin(), user.inputs.end(), value) != user.inputs.end();
                 if (reads) candidate = false;
@@ -382,9 +510,17 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
             out.steps.push_back(std::move(s));
         }
     }
+    if (options.fuse_rows) fuse_row_runs(graph, &out.steps);
     if (options.rematerialize) rematerialize_for_reductions(graph, &out.steps);
+    std::vector<bool> f32_only(count, false);  // values whose producing kernel writes FP32 and nothing else
     for (std::size_t i = 0; i < out.steps.size(); ++i) {
-        step_of[static_cast<std::size_t>(out.steps[i].result)] = static_cast<std::int32_t>(i);
+        const Step& s = out.steps[i];
+        step_of[static_cast<std::size_t>(s.result)] = static_cast<std::int32_t>(i);
+        if (s.kind == Step::Kind::Reduce) f32_only[static_cast<std::size_t>(s.result)] = true;
+        for (NodeId w : s.row_outputs) {
+            step_of[static_cast<std::size_t>(w)] = static_cast<std::int32_t>(i);
+            f32_only[static_cast<std::size_t>(w)] = true;
+        }
     }
 
     // What form each value is read in.
@@ -419,7 +555,7 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
             if (step_of[i] < 0) continue;  // a folded matmul or an absorbed producer has no value of its own
             for (Rep rep : {kRepHalf, kRepHalfT, kRepF32T}) {
                 if (!needs[rep]) continue;
-                if (rep == kRepHalf && !is_row_reduce(n.op)) continue;  // written by the producing kernel itself
+                if (rep == kRepHalf && !f32_only[i]) continue;  // written by the producing kernel itself
                 needs[kRepF32] = true;
                 out.after_step[static_cast<std::size_t>(step_of[i])].push_back({id, rep});
             }
@@ -439,7 +575,7 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
     for (Step& s : out.steps) {
         const auto& needs = out.needs[static_cast<std::size_t>(s.result)];
         s.write_f32 = needs[kRepF32];
-        s.write_half = needs[kRepHalf] && s.kind != Step::Kind::Reduce ? out.half_kind : HalfKind::None;
+        s.write_half = needs[kRepHalf] && !f32_only[static_cast<std::size_t>(s.result)] ? out.half_kind : HalfKind::None;
     }
 
     // Launch count and the shared split-K workspace.
@@ -466,9 +602,13 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
     for (std::size_t i = 0; i < out.steps.size(); ++i) {
         const Step& s = out.steps[i];
         PoolStep ps;
-        for (int rep = 0; rep < kNumReps; ++rep) {
-            if (out.needs[static_cast<std::size_t>(s.result)][static_cast<std::size_t>(rep)]) {
-                ps.defines.push_back(value_index(s.result, static_cast<Rep>(rep)));
+        std::vector<NodeId> defined = s.row_outputs;
+        if (defined.empty()) defined.push_back(s.result);
+        for (NodeId d : defined) {
+            for (int rep = 0; rep < kNumReps; ++rep) {
+                if (out.needs[static_cast<std::size_t>(d)][static_cast<std::size_t>(rep)]) {
+                    ps.defines.push_back(value_index(d, static_cast<Rep>(rep)));
+                }
             }
         }
         if (s.kind != Step::Kind::Matmul) {
@@ -603,6 +743,10 @@ std::string describe(const Graph& graph, const LoweredGraph& lowered) {
         os << i << ": ";
         if (s.kind == Step::Kind::Elementwise) {
             os << "elementwise " << graph.node(s.result).name << " ops=" << s.program.num_ops();
+        } else if (s.kind == Step::Kind::RowFused) {
+            os << "row_fused";
+            for (const RowPart& part : s.row_parts) os << " " << part.name << (part.output >= 0 ? "*" : "");
+            os << " rows of " << s.reduce_shape.back() << " reads=" << s.inputs.size() << " writes=" << s.row_outputs.size();
         } else if (s.kind == Step::Kind::Reduce) {
             os << op_name(s.reduce_op) << " " << graph.node(s.result).name << " rows of " << s.reduce_shape.back()
                << " prologue_ops=" << s.program.num_ops();

@@ -83,6 +83,7 @@ struct CudaOptions {
     // 256-thread blocks with four 128-bit loads in flight per thread stream faster than eight (6.1 vs
     // 5.5 TB/s on the 512 MiB GELU pass): more outstanding requests than that only queue up in front of HBM.
     int eltwise_blocks_per_sm = 4;
+    bool fuse_rows = true;      // runs of steps on rows of one shape become one kernel (reduce_codegen.hpp)
     bool rematerialize = true;  // recompute cheap elementwise values read by a row reduction in each reader
 };
 
@@ -98,7 +99,7 @@ struct EpilogueOperand {
 };
 
 struct Step {
-    enum class Kind { Elementwise, Matmul, Reduce };
+    enum class Kind { Elementwise, Matmul, Reduce, RowFused };
     Kind kind = Kind::Elementwise;
     NodeId result = kNoNode;  // the node whose value this step defines
 
@@ -112,6 +113,12 @@ struct Step {
 
     OpKind reduce_op = OpKind::RowSum;
     Shape reduce_shape;
+    // RowFused: a run of Elementwise / Reduce steps on rows of `reduce_shape`, generated as one kernel
+    // (reduce_codegen.hpp). `inputs` are the values it reads from memory, `row_outputs` the values it writes
+    // (`result` is the first of them); values used only inside the run never exist in memory.
+    std::vector<RowPart> row_parts;
+    std::vector<RowOperand::Kind> row_externals;  // per entry of `inputs`
+    std::vector<NodeId> row_outputs;
 
     NodeId matmul = kNoNode;
     NodeId lhs = kNoNode;

@@ -33,3 +33,42 @@ RowReduceKernel generate_row_reduce_kernel(OpKind reduce_op, const FusedProgram&
                                            const std::vector<Shape>& input_shapes, const Shape& in_shape);
 
 }  // namespace minicompiler::cuda
+
+// ---------------------------------------------------------------- whole rows in one kernel
+//
+// A run of steps that all work on rows of one shape [.., N] - elementwise steps on the full shape, row reductions,
+// elementwise steps on the reduced [.., 1] values - is generated as ONE kernel: a 256-thread block owns a row, keeps
+// every full-shaped value in registers (N / 256 elements per thread), gets reduced values by a block reduction and
+// runs the steps in their original order, so x is read once and y written once (softmax, LayerNorm: two tensor
+// passes instead of four). The reduction order is exactly that of `mc_row_reduce` with 256 threads per row, so a
+// fused run gives the bits of the separate kernels.
+
+namespace minicompiler::cuda {
+
+inline constexpr const char* kRowFusedKernelName = "mc_row_fused";
+inline constexpr std::int64_t kRowFusedMinWidth = 1024;  // below this the separate reduction uses one warp per row
+inline constexpr std::int64_t kRowFusedMaxWidth = 8192;  // 32 registers per full-shaped value and thread
+
+struct RowOperand {
+    enum class Kind { Full, PerRow, RowVector, Scalar };
+    Kind kind = Kind::Full;
+    int external = -1;  // index into the kernel's external pointers, or
+    int value = -1;     // the `result` number of an earlier part
+};
+
+struct RowPart {
+    bool is_reduce = false;
+    OpKind reduce_op = OpKind::RowSum;
+    FusedProgram program;              // over `operands`
+    std::vector<RowOperand> operands;
+    int result = 0;                    // value number this part defines
+    bool result_is_full = true;        // false: one value per row (a reduction, or elementwise on reduced values)
+    int output = -1;                   // index into the kernel's output pointers when the value is written
+    std::string name;                  // for the comment line
+};
+
+// Kernel parameters: out0, out1, ..., ex0, ex1, ..., unsigned rows.
+std::string generate_row_fused_kernel(const std::vector<RowPart>& parts, const std::vector<RowOperand::Kind>& externals,
+                                      int num_outputs, std::int64_t width);
+
+}  // namespace minicompiler::cuda

@@ -115,6 +115,8 @@ Status parse_options(const char* text, cuda::CudaOptions* options) {
                 options->streaming_hints = number != 0;
             } else if (key == "gemm_variant") {
                 options->gemm_variant = static_cast<int>(number);
+            } else if (key == "fuse_rows") {
+                options->fuse_rows = number != 0;
             } else if (key == "rematerialize") {
                 options->rematerialize = number != 0;
             } else if (key == "host_io") {
@@ -127,7 +129,7 @@ Status parse_options(const char* text, cuda::CudaOptions* options) {
                 options->eltwise_blocks_per_sm = static_cast<int>(number);
             } else {
                 return Error{"unknown option '" + key +
-                             "' (device, matmul, vectorize, fuse_epilogue, b_layout, unroll, streaming, gemm_variant, fmad, blocks_per_sm, graph, host_io, rematerialize)"};
+                             "' (device, matmul, vectorize, fuse_epilogue, b_layout, unroll, streaming, gemm_variant, fmad, blocks_per_sm, graph, host_io, rematerialize, fuse_rows)"};
             }
         }
     }
@@ -496,6 +498,39 @@ long long mcb_graph_constant(const void* graph, const char* name, float* out, lo
 
 int mcd_jit_compile_only(const char* source, const char* options, size_t* cubin_bytes);
 
+namespace {
+
+// The text generated for one step of a launch plan: the kernel of an elementwise, reduction or row-fused step, the
+// epilogue plus kernel family of a matmul with a fused consumer; empty for a matmul that runs a built-in kernel.
+std::string step_source(const Graph& g, const cuda::CudaOptions& parsed, const cuda::Step& step) {
+    std::vector<Shape> shapes;
+    for (NodeId in : step.inputs) shapes.push_back(g.node(in).type.shape);
+    switch (step.kind) {
+        case cuda::Step::Kind::Elementwise: {
+            cuda::ElementwiseOptions eo;
+            eo.allow_vectorize = parsed.vectorize;
+            eo.unroll = parsed.eltwise_unroll;
+            eo.write_f32 = step.write_f32;
+            eo.write_half = step.write_half;
+            eo.streaming_hints = parsed.streaming_hints;
+            const TensorType& type = g.node(step.result).type;
+            if (step.write_half != cuda::HalfKind::None && type.shape.size() == 2) eo.half_pitch = cuda::half_pitch(type.shape[1]);
+            return cuda::generate_elementwise_kernel(step.program, shapes, type.shape, eo).source;
+        }
+        case cuda::Step::Kind::RowFused:
+            return cuda::generate_row_fused_kernel(step.row_parts, step.row_externals, static_cast<int>(step.row_outputs.size()),
+                                                   step.reduce_shape.back());
+        case cuda::Step::Kind::Reduce:
+            return cuda::generate_row_reduce_kernel(step.reduce_op, step.program, shapes, step.reduce_shape).source;
+        case cuda::Step::Kind::Matmul:
+            if (!step.has_epilogue) return {};
+            return cuda::generate_epilogue_source(g, step) + mcd_gemm_source(step.splits > 1 ? -1 : static_cast<int>(step.arith));
+    }
+    return {};
+}
+
+}  // namespace
+
 int mcb_graph_check_kernels(const void* graph, const char* options, int sm_count) {
     const Graph& g = static_cast<const OpenGraph*>(graph)->graph;
     cuda::CudaOptions parsed;
@@ -523,41 +558,40 @@ int mcb_graph_check_kernels(const void* graph, const char* options, int sm_count
         return true;
     };
     for (const cuda::Step& step : lowered->steps) {
-        std::string source;
-        if (step.kind == cuda::Step::Kind::Elementwise) {
-            std::vector<Shape> shapes;
-            for (NodeId in : step.inputs) shapes.push_back(g.node(in).type.shape);
-            cuda::ElementwiseOptions eo;
-            eo.allow_vectorize = parsed.vectorize;
-            eo.unroll = parsed.eltwise_unroll;
-            eo.write_f32 = step.write_f32;
-            eo.write_half = step.write_half;
-            eo.streaming_hints = parsed.streaming_hints;
-            const TensorType& type = g.node(step.result).type;
-            if (step.write_half != cuda::HalfKind::None && type.shape.size() == 2) eo.half_pitch = cuda::half_pitch(type.shape[1]);
-            source = cuda::generate_elementwise_kernel(step.program, shapes, type.shape, eo).source;
-        } else if (step.kind == cuda::Step::Kind::Reduce) {
-            std::vector<Shape> shapes;
-            for (NodeId in : step.inputs) shapes.push_back(g.node(in).type.shape);
-            source = cuda::generate_row_reduce_kernel(step.reduce_op, step.program, shapes, step.reduce_shape).source;
-        } else if (step.has_epilogue) {
-            source = cuda::generate_epilogue_source(g, step) +
-                     mcd_gemm_source(step.splits > 1 ? -1 : static_cast<int>(step.arith));
-            if (step.splits == 1 && step.arith != cuda::Arith::F32) {
-                const bool tf32 = step.arith == cuda::Arith::Tf32;
-                for (const char* entry : {tf32 ? "mc_gemm_tc_tf32_bk" : "mc_gemm_tc_h16_bmn",
-                                          tf32 ? "mc_gemm_tc2_tf32_bk" : "mc_gemm_tc2_h16_bk",
-                                          tf32 ? "mc_gemm_tc2w_tf32_bk" : "mc_gemm_tc2w_h16_bmn"}) {
-                    if (!compile_once(std::string("#define MC_SINGLE_ENTRY 1\n#define MC_ONLY_") + entry + " 1\n" + source)) return 1;
-                }
-                continue;
+        const std::string source = step_source(g, parsed, step);
+        if (source.empty()) continue;
+        if (step.kind == cuda::Step::Kind::Matmul && step.splits == 1 && step.arith != cuda::Arith::F32) {
+            const bool tf32 = step.arith == cuda::Arith::Tf32;
+            for (const char* entry : {tf32 ? "mc_gemm_tc_tf32_bk" : "mc_gemm_tc_h16_bmn", tf32 ? "mc_gemm_tc2_tf32_bk" : "mc_gemm_tc2_h16_bk",
+                                      tf32 ? "mc_gemm_tc2w_tf32_bk" : "mc_gemm_tc2w_h16_bmn"}) {
+                if (!compile_once(std::string("#define MC_SINGLE_ENTRY 1\n#define MC_ONLY_") + entry + " 1\n" + source)) return 1;
             }
-        } else {
             continue;
         }
         if (!compile_once(source)) return 1;
     }
     return 0;
+}
+
+int mcb_graph_plan_sources(const void* graph, const char* options, int sm_count, char* out, int size) {
+    const Graph& g = static_cast<const OpenGraph*>(graph)->graph;
+    cuda::CudaOptions parsed;
+    if (failed(parse_options(options, &parsed))) return -1;
+    Result<cuda::LoweredGraph> lowered = cuda::lower_graph(g, parsed, sm_count);
+    if (!lowered.ok()) {
+        g_error = lowered.error().message;
+        return -1;
+    }
+    std::string text;
+    for (std::size_t i = 0; i < lowered->steps.size(); ++i) {
+        const cuda::Step& step = lowered->steps[i];
+        if (step.kind == cuda::Step::Kind::Matmul) {
+            if (step.has_epilogue) text += "// step " + std::to_string(i) + "\n" + cuda::generate_epilogue_source(g, step) + "\n";
+            continue;
+        }
+        text += "// step " + std::to_string(i) + "\n" + step_source(g, parsed, step) + "\n";
+    }
+    return put_len(out, size, text);
 }
 
 void mcb_uniform_values(float* out, long long count, unsigned long long seed, float lo, float hi) {

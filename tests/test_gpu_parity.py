@@ -485,7 +485,7 @@ def test_row_reduction_with_an_absorbed_broadcasting_producer(mc, oracle):
             "s = row_sum v\nm = row_max v\noutput s, m")
     g, ins = oracle_inputs(oracle, text, seed=9, lo=-1.0, hi=1.0)
     want_s, want_m = oracle.evaluate_f64(g, ins)
-    for options, launches in [({}, 2), ({"rematerialize": 0}, 3)]:
+    for options, launches in [({}, 2), ({"rematerialize": 0}, 3)]:  # rows of 700 stay below the row-kernel range
         # exp(...) has two readers: by default each reduction recomputes it, otherwise it is written once
         with mc.CompiledGraph(text=text, options=options) as exe:
             got_s, got_m = exe.run(ins)
@@ -504,17 +504,42 @@ def test_row_reduction_with_an_absorbed_broadcasting_producer(mc, oracle):
 
 
 def test_softmax_and_layernorm_graphs(mc, oracle):
-    for name, dims in [("x1_softmax", "M=128,N=1000"), ("x1_softmax", "M=64,N=4096"), ("x2_layernorm", "M=96,N=4096")]:
+    for name, dims in [("x1_softmax", "M=128,N=1000"), ("x1_softmax", "M=64,N=4096"), ("x2_layernorm", "M=96,N=4096"),
+                       ("x1_softmax", "M=300,N=5000"), ("x1_softmax", "M=7,N=8192"), ("x1_softmax", "M=33,N=16384")]:
         path = mc.graph_path(name)
         g, _ = oracle_inputs(oracle, path=path, dims=dims)
         x = oracle.normal_values(int(np.prod(g.node(g.inputs[0]).shape)), 7)
         want = oracle.evaluate_f64(g, [x])[0]
         with mc.CompiledGraph(path, dims=dims) as exe:
             got = exe.run([x])[0]
-        with mc.CompiledGraph(path, dims=dims, options={"rematerialize": 0}) as exe:
-            written = exe.run([x])[0]
-        assert np.array_equal(got, written)  # recomputing a value performs the same operations per element
+            fused_launches = exe.kernel_launches
+        width = int(dims.split("N=")[1])
+        assert fused_launches == (1 if 1024 <= width <= 8192 else 3)  # whole rows in one kernel when they fit
+        for options in ({"fuse_rows": 0}, {"fuse_rows": 0, "rematerialize": 0}):
+            with mc.CompiledGraph(path, dims=dims, options=options) as exe:
+                separate = exe.run([x])[0]
+            # the row kernel and the recomputing form perform the same operations per element in the same order
+            assert np.array_equal(got, separate), f"{name} {dims} {options}"
         assert norm_scaled_error(got, want) <= 1e-5, f"{name} {dims}: {norm_scaled_error(got, want):.2e}"
         if name == "x1_softmax":
-            width = int(dims.split("N=")[1])
             assert np.allclose(got.reshape(-1, width).sum(axis=1), 1.0, atol=1e-5)
+
+
+def test_row_kernel_with_several_outputs_and_operand_kinds(mc, oracle):
+    """One row-fused kernel reading a full tensor, a per-row column, a row vector and a scalar, and writing a
+    full-shaped and two per-row values; against the oracle and, bit for bit, against the separate kernels."""
+    text = ("input x : f32[5, 6, 1500]\ninput col : f32[5, 6, 1]\ninput vec : f32[1500]\nconst k : f32[] = 0.5\n"
+            "a = mul x, vec\nb = add a, col\nm = row_max b\nd = sub b, m\ne = exp d\ns = row_sum e\nh = mul s, k\n"
+            "y = div e, h\noutput y, m, h")
+    g, ins = oracle_inputs(oracle, text, seed=4, lo=-1.0, hi=1.0)
+    want = oracle.evaluate_f64(g, ins)
+    with mc.CompiledGraph(text=text) as exe:
+        got = exe.run(ins)
+        assert exe.kernel_launches == 1
+    with mc.CompiledGraph(text=text, options={"fuse_rows": 0}) as exe:
+        separate = exe.run(ins)
+        assert exe.kernel_launches > 1
+    for g_, s_, w_ in zip(got, separate, want):
+        assert np.array_equal(g_, s_)
+        ok, msg = all_close(g_, w_, 2e-5, 1e-7)
+        assert ok, msg
