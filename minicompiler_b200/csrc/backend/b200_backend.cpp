@@ -629,7 +629,9 @@ private:
         int blocks_per_sm = 0;
         MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(kRowReduceBlock), 0, &blocks_per_sm));
         const std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
-        launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(rows, resident)));
+        const std::size_t rows_per_block = step.reduce_shape.back() >= 1024 ? 1 : kRowReduceBlock / 32;
+        const std::size_t wanted = (rows + rows_per_block - 1) / rows_per_block;
+        launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(wanted, resident)));
         for (NodeId w : step.row_outputs) {
             launch->pointers.push_back(address(w, kRepF32));
             launch->advances.push_back(0);

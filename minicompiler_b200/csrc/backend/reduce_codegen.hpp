@@ -37,16 +37,16 @@ RowReduceKernel generate_row_reduce_kernel(OpKind reduce_op, const FusedProgram&
 // ---------------------------------------------------------------- whole rows in one kernel
 //
 // A run of steps that all work on rows of one shape [.., N] - elementwise steps on the full shape, row reductions,
-// elementwise steps on the reduced [.., 1] values - is generated as ONE kernel: a 256-thread block owns a row, keeps
-// every full-shaped value in registers (N / 256 elements per thread), gets reduced values by a block reduction and
-// runs the steps in their original order, so x is read once and y written once (softmax, LayerNorm: two tensor
-// passes instead of four). The reduction order is exactly that of `mc_row_reduce` with 256 threads per row, so a
-// fused run gives the bits of the separate kernels.
+// elementwise steps on the reduced [.., 1] values - is generated as ONE kernel: a 256-thread block (a warp, for rows
+// below 1024 elements) owns a row, keeps every full-shaped value in registers (N / 256, or N / 32, elements per
+// thread), gets reduced values by a block (warp) reduction and runs the steps in their original order, so x is read
+// once and y written once (softmax, LayerNorm: two tensor passes instead of four). The reduction order is exactly
+// that of `mc_row_reduce` for the same row length, so a fused run gives the bits of the separate kernels.
 
 namespace minicompiler::cuda {
 
 inline constexpr const char* kRowFusedKernelName = "mc_row_fused";
-inline constexpr std::int64_t kRowFusedMinWidth = 1024;  // below this the separate reduction uses one warp per row
+inline constexpr std::int64_t kRowFusedMinWidth = 2;     // rows below 1024 elements take one warp, as in mc_row_reduce
 inline constexpr std::int64_t kRowFusedMaxWidth = 8192;  // 32 registers per full-shaped value and thread
 
 struct RowOperand {

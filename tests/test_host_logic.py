@@ -483,7 +483,7 @@ def test_constant_row_reductions_fold_to_known_answers(mc):
 
 
 def test_row_reduction_lowering_absorbs_and_rematerializes_producers(mc):
-    separate = {"fuse_rows": 0}  # the per-step form; rows of 1024 to 8192 elements otherwise become one kernel
+    separate = {"fuse_rows": 0}  # the per-step form; rows of up to 8192 elements otherwise become one kernel
     g = mc.HostGraph(mc.graph_path("x2_layernorm"), dims="M=64,N=4096")
     plain = g.launch_plan({"rematerialize": 0, **separate})
     assert "row_sum total rows of 4096 prologue_ops=0" in plain
@@ -498,8 +498,9 @@ def test_row_reduction_lowering_absorbs_and_rematerializes_producers(mc):
     assert "launches=4 " in soft.launch_plan({"rematerialize": 0, **separate})
     assert "row_sum s rows of 4096 prologue_ops=2" in soft.launch_plan(separate) and "launches=3 " in soft.launch_plan(separate)
     # an output is written in any case; graphs without reductions are lowered as before
-    kept = mc.HostGraph(text="input x : f32[8, 64]\ne = exp x\ns = row_sum e\noutput s, e").launch_plan({})
-    assert "prologue_ops=0" in kept and "elementwise e" in kept
+    kept = mc.HostGraph(text="input x : f32[8, 64]\ne = exp x\ns = row_sum e\noutput s, e")
+    assert "prologue_ops=0" in kept.launch_plan(separate) and "elementwise e" in kept.launch_plan(separate)
+    assert "row_fused e* s* rows of 64 reads=1 writes=2" in kept.launch_plan({})
     chain = mc.HostGraph(str(GOLDEN / "graphs" / "ref_gelu_chain.mcg"), dims="M=64,N=64", passes="none")
     assert chain.launch_plan({}) == chain.launch_plan({"rematerialize": 0, **separate})
 
@@ -515,15 +516,17 @@ def test_runs_of_row_steps_become_one_kernel(mc):
     assert "mc_row_fused(float* __restrict__ out0, const float* __restrict__ ex0" in src
     assert src.count("__syncthreads();") == 4 and "__ldg(ex2 + col)" in src and "const float s1 = ex1[0];" in src
     assert src.count("__ldcs(ex0 + base + col)") == 1 and src.count("__stcs(out0 + base + col") == 1  # x read once, y written once
-    # narrow rows keep the warp-per-row kernels, very wide rows would not fit in registers
-    assert "row_fused" not in mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=1000").launch_plan({})
+    # rows below 1024 elements take a warp each, very wide rows would not fit in registers and stay separate kernels
+    short = mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=1000")
+    assert "row_fused" in short.launch_plan({}) and "32 threads per row, 32 element(s) per thread" in short.plan_sources({})
+    assert "__syncthreads" not in short.plan_sources({})
     assert "row_fused" not in mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=16384").launch_plan({})
     # values that something outside the run reads are written; a matmul ends a run
     text = ("input x : f32[64, 2048]\nconst w : f32[2048, 64] = uniform(seed=3, lo=-1, hi=1)\nm = row_max x\nd = sub x, m\n"
             "e = exp d\ns = row_sum e\ny = div e, s\nz = matmul y, w\noutput z, s")
     plan = mc.HostGraph(text=text).launch_plan({})
     assert "row_fused m e s* y* rows of 2048 reads=1 writes=2" in plan and "matmul z" in plan
-    for g in (soft, norm, mc.HostGraph(text=text), mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=3,N=5000")):
+    for g in (soft, norm, short, mc.HostGraph(text=text), mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=3,N=5000")):
         g.check_kernels({})
 
 
