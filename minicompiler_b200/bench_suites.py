@@ -1,6 +1,6 @@
 """The reference's GPU benchmark suites, re-hosted on this backend (needs a B200).
 
-    python -m minicompiler_b200.bench_suites --suite elementwise|matmul|tensor_core|all [--out FILE]
+    python -m minicompiler_b200.bench_suites --suite elementwise|matmul|tensor_core|rows|all [--out FILE]
 
 They follow bench/bench_cuda.cpp of the reference:
   elementwise   the GELU chain at M in {1,16,256,1024,4096,16384}, N=4096, unfused (passes
@@ -8,6 +8,8 @@ They follow bench/bench_cuda.cpp of the reference:
                 moves, speed-up (run_elementwise, bench_cuda.cpp:182-288).
   matmul        the FP32 kernel against cuBLAS SGEMM on square and split-K shapes (run_matmul, :543-673).
   tensor_core   the tcgen05 kernels against cuBLAS in the same format (run_tensor_core, :700-851).
+  rows          (no counterpart in the reference) softmax and LayerNorm graphs built from the row reductions
+                against torch's kernels.
 Every variant is checked before it is timed: 1000 sampled outputs against float64 dot products
 (the method of run_and_check, :386-436). cuBLAS is reached through torch.matmul and is a comparison
 column only, never part of the product. Times are CUDA events around `mc_enqueue` on a side stream,
@@ -165,9 +167,50 @@ def suite_tensor_core(mc, rounds):
     return _gemm_rows(mc, rounds, shapes, kernels)
 
 
+def suite_rows(mc, rounds):
+    """The extension graphs built from row reductions (softmax, LayerNorm over the last dimension) against
+    torch.softmax / torch.nn.functional.layer_norm: time, and bandwidth from read x + write y. Each result is
+    checked against a float64 computation of the same rows first."""
+    import torch
+
+    stream = torch.cuda.Stream()
+    rows = []
+    for name, m, n in [("x1_softmax", 8192, 128), ("x1_softmax", 8192, 1024), ("x1_softmax", 8192, 4096), ("x1_softmax", 8192, 8192),
+                       ("x1_softmax", 4096, 16384), ("x2_layernorm", 16384, 4096), ("x2_layernorm", 65536, 4096)]:
+        x = np.random.default_rng(2).standard_normal(m * n, dtype=np.float32)
+        t = torch.from_numpy(x).cuda().reshape(m, n)
+        with mc.CompiledGraph(mc.graph_path(name), dims={"M": m, "N": n}) as exe:
+            exe.upload([x])
+            exe.enqueue(stream.cuda_stream)
+            got = exe.download()[0].reshape(m, n)
+            launches = exe.kernel_launches
+            sample = got[:: max(1, m // 64)].astype(np.float64)
+            x64 = x.reshape(m, n)[:: max(1, m // 64)].astype(np.float64)
+            if name == "x1_softmax":
+                e = np.exp(x64 - x64.max(axis=1, keepdims=True))
+                want = e / e.sum(axis=1, keepdims=True)
+                lib = lambda: torch.softmax(t, dim=-1)  # noqa: E731
+            else:
+                gamma = mc.HostGraph(mc.graph_path(name), dims={"M": 1, "N": n}, passes="none").constant("gamma").astype(np.float64)
+                beta = mc.HostGraph(mc.graph_path(name), dims={"M": 1, "N": n}, passes="none").constant("beta").astype(np.float64)
+                mean = x64.sum(axis=1, keepdims=True) / 4096.0  # the graph's constant 1/4096, whatever N is
+                c = x64 - mean
+                want = c / np.sqrt((c * c).sum(axis=1, keepdims=True) / 4096.0 + 1e-5) * gamma + beta
+                lib = lambda: torch.nn.functional.layer_norm(t, (n,))  # noqa: E731
+            assert np.allclose(sample, want, rtol=2e-5, atol=1e-6), f"{name} {m}x{n}"
+            small = m * n * 8 < (200 << 20)
+            ms = _median_ms(lambda: exe.enqueue(stream.cuda_stream), stream, rounds, small)
+        with torch.cuda.stream(stream):
+            lib_ms = _median_ms(lib, stream, rounds, small)
+        moved = 2 * 4 * m * n
+        rows.append({"graph": name, "M": m, "N": n, "launches": launches, "ms": ms, "gbs": moved / ms / 1e6, "torch_ms": lib_ms,
+                     "torch_gbs": moved / lib_ms / 1e6, "pct_of_torch": 100.0 * lib_ms / ms})
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--suite", default="all", choices=["elementwise", "matmul", "tensor_core", "all"])
+    ap.add_argument("--suite", default="all", choices=["elementwise", "matmul", "tensor_core", "rows", "all"])
     ap.add_argument("--rounds", type=int, default=30)
     ap.add_argument("--out", default="")
     args = ap.parse_args()
@@ -184,6 +227,8 @@ def main():
         result["matmul"] = suite_matmul(mc, args.rounds)
     if args.suite in ("tensor_core", "all"):
         result["tensor_core"] = suite_tensor_core(mc, args.rounds)
+    if args.suite in ("rows", "all"):
+        result["rows"] = suite_rows(mc, args.rounds)
     text = json.dumps(result, indent=1)
     if args.out:
         Path(args.out).write_text(text)
