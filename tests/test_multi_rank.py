@@ -39,7 +39,7 @@ def _rank_main(rank: int, world: int, port: int, graph: str, dims: str, batch_di
     whole = oracle.parse_mcg_file(path, full_dims)
 
     # one broadcast replicates the constants (here: checks that they were identical to begin with)
-    consts = np.concatenate([n.value.reshape(-1) for n in g.nodes if n.op == "const"])
+    consts = np.concatenate([np.zeros(1, dtype=np.float32)] + [n.value.reshape(-1) for n in g.nodes if n.op == "const"])
     t = torch.from_numpy(consts.copy())
     dist.broadcast(t, src=0)
     assert np.array_equal(t.numpy(), consts)
@@ -59,7 +59,8 @@ def _rank_main(rank: int, world: int, port: int, graph: str, dims: str, batch_di
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("graph,dims,batch_dim", [("c5_mlp_stack", "B=32,D=64", "B"), ("c3_ffn", "T=16,D=32,H=64", "T")])
+@pytest.mark.parametrize("graph,dims,batch_dim", [("c5_mlp_stack", "B=32,D=64", "B"), ("c3_ffn", "T=16,D=32,H=64", "T"),
+                                                  ("x1_softmax", "M=16,N=96", "M")])
 def test_row_shards_assemble_to_the_unsharded_result(tmp_path, graph, dims, batch_dim):
     import torch.multiprocessing as mp
 
