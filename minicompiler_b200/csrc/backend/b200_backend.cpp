@@ -36,6 +36,7 @@ struct Launch {
     // Elementwise: an NVRTC-compiled kernel; params = [out] [out16] in... n
     void* function = nullptr;
     unsigned grid = 0;
+    unsigned block = kElementwiseBlock;
     unsigned count = 0;
     std::vector<void*> pointers;
     std::vector<char> advances;  // per pointer: 1 when it walks the tensor element by element (output, same-size inputs)
@@ -368,7 +369,7 @@ private:
     Status issue(const Launch& l, void* stream) const {
         switch (l.kind) {
             case Launch::Kind::Elementwise:
-                MCD_TRY(mcd_launch(l.function, l.grid, 1, 1, kElementwiseBlock, 0, stream, const_cast<void**>(l.params.data())));
+                MCD_TRY(mcd_launch(l.function, l.grid, 1, 1, l.block, 0, stream, const_cast<void**>(l.params.data())));
                 return Status();
             case Launch::Kind::Matmul: MCD_TRY(mcd_gemm(&l.gemm, stream)); return Status();
             case Launch::Kind::Recast:
@@ -595,8 +596,9 @@ private:
 
         const std::size_t rows = node.type.num_elements();
         launch->count = static_cast<unsigned>(rows);
+        launch->block = kernel.block;
         int blocks_per_sm = 0;
-        MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(kRowReduceBlock), 0, &blocks_per_sm));
+        MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(kernel.block), 0, &blocks_per_sm));
         const std::size_t wanted = (rows + kernel.rows_per_block - 1) / kernel.rows_per_block;
         const std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
         launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(wanted, resident)));
@@ -626,10 +628,11 @@ private:
         sources_.push_back(source);
         const std::size_t rows = num_elements(step.reduce_shape) / static_cast<std::size_t>(step.reduce_shape.back());
         launch->count = static_cast<unsigned>(rows);
+        launch->block = row_block(step.reduce_shape.back());
         int blocks_per_sm = 0;
-        MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(kRowReduceBlock), 0, &blocks_per_sm));
+        MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(launch->block), 0, &blocks_per_sm));
         const std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
-        const std::size_t rows_per_block = step.reduce_shape.back() >= 1024 ? 1 : kRowReduceBlock / 32;
+        const std::size_t rows_per_block = launch->block / row_threads(step.reduce_shape.back());
         const std::size_t wanted = (rows + rows_per_block - 1) / rows_per_block;
         launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(wanted, resident)));
         for (NodeId w : step.row_outputs) {

@@ -9,8 +9,8 @@
 // Kernel contract: `mc_row_reduce(float* out, in0, in1, ..., unsigned rows)`. The program is evaluated for every
 // element of the pre-reduction shape `in_shape` (its inputs broadcast against that shape), and the values of each
 // row of the last dimension are combined: per thread in increasing column order, then across the lanes of a warp
-// by an xor-shuffle tree, then (rows of 1024 elements or more, one 256-thread block per row) across the 8 warps
-// in warp order. The order is fixed, so results do not depend on scheduling. Sums are FP32 (the definition of the
+// by an xor-shuffle tree, then (rows of 1024 elements or more, one block per row) across the block's warps in
+// warp order. The order is fixed, so results do not depend on scheduling. Sums are FP32 (the definition of the
 // op is the double-precision sum rounded once; the kernel is within n*2^-24 * sum|x| of it); maxima are exact.
 
 #include "core/ir.hpp"
@@ -23,10 +23,19 @@ namespace minicompiler::cuda {
 inline constexpr const char* kRowReduceKernelName = "mc_row_reduce";
 inline constexpr unsigned kRowReduceBlock = 256;
 
+// Threads that share a row, for both kernels of this file: a warp below 1024 elements (8 rows per 256-thread
+// block), a 256-thread block up to 8192, a 512-thread block up to 16384 (so that a row still fits the registers of
+// the row-fused kernel), 256 beyond.
+inline unsigned row_threads(std::int64_t width) {
+    return width < 1024 ? 32u : width <= 8192 ? 256u : width <= 16384 ? 512u : 256u;
+}
+inline unsigned row_block(std::int64_t width) { return row_threads(width) > kRowReduceBlock ? row_threads(width) : kRowReduceBlock; }
+
 struct RowReduceKernel {
     std::string source;
-    unsigned threads_per_row = 32;  // 32: eight rows per block, one warp each; 256: one row per block
+    unsigned threads_per_row = 32;  // row_threads(width)
     unsigned rows_per_block = 8;
+    unsigned block = kRowReduceBlock;  // threads per block to launch with
 };
 
 RowReduceKernel generate_row_reduce_kernel(OpKind reduce_op, const FusedProgram& program,
@@ -47,7 +56,7 @@ namespace minicompiler::cuda {
 
 inline constexpr const char* kRowFusedKernelName = "mc_row_fused";
 inline constexpr std::int64_t kRowFusedMinWidth = 2;     // rows below 1024 elements take one warp, as in mc_row_reduce
-inline constexpr std::int64_t kRowFusedMaxWidth = 8192;  // 32 registers per full-shaped value and thread
+inline constexpr std::int64_t kRowFusedMaxWidth = 16384;  // at most 32 registers per full-shaped value and thread
 
 struct RowOperand {
     enum class Kind { Full, PerRow, RowVector, Scalar };

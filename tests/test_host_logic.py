@@ -483,7 +483,7 @@ def test_constant_row_reductions_fold_to_known_answers(mc):
 
 
 def test_row_reduction_lowering_absorbs_and_rematerializes_producers(mc):
-    separate = {"fuse_rows": 0}  # the per-step form; rows of up to 8192 elements otherwise become one kernel
+    separate = {"fuse_rows": 0}  # the per-step form; rows of up to 16384 elements otherwise become one kernel
     g = mc.HostGraph(mc.graph_path("x2_layernorm"), dims="M=64,N=4096")
     plain = g.launch_plan({"rematerialize": 0, **separate})
     assert "row_sum total rows of 4096 prologue_ops=0" in plain
@@ -520,13 +520,16 @@ def test_runs_of_row_steps_become_one_kernel(mc):
     short = mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=1000")
     assert "row_fused" in short.launch_plan({}) and "32 threads per row, 32 element(s) per thread" in short.plan_sources({})
     assert "__syncthreads" not in short.plan_sources({})
-    assert "row_fused" not in mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=16384").launch_plan({})
+    wide = mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=16384")
+    assert "row_fused" in wide.launch_plan({}) and "__launch_bounds__(512)" in wide.plan_sources({})
+    assert "__launch_bounds__(512)" in wide.plan_sources({"fuse_rows": 0})  # the separate reduction shares the row's thread count
+    assert "row_fused" not in mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=20000").launch_plan({})
     # values that something outside the run reads are written; a matmul ends a run
     text = ("input x : f32[64, 2048]\nconst w : f32[2048, 64] = uniform(seed=3, lo=-1, hi=1)\nm = row_max x\nd = sub x, m\n"
             "e = exp d\ns = row_sum e\ny = div e, s\nz = matmul y, w\noutput z, s")
     plan = mc.HostGraph(text=text).launch_plan({})
     assert "row_fused m e s* y* rows of 2048 reads=1 writes=2" in plan and "matmul z" in plan
-    for g in (soft, norm, short, mc.HostGraph(text=text), mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=3,N=5000")):
+    for g in (soft, norm, short, wide, mc.HostGraph(text=text), mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=3,N=5000")):
         g.check_kernels({})
 
 
