@@ -545,3 +545,68 @@ def test_row_kernel_with_several_outputs_and_operand_kinds(mc, oracle):
         assert np.array_equal(g_, s_)
         ok, msg = all_close(g_, w_, 2e-5, 1e-7)
         assert ok, msg
+
+
+def _random_row_graph(rng, rows_shape):
+    """A random graph of elementwise steps on `rows_shape`, row reductions and per-row steps, with full-shaped,
+    per-row, row-vector and scalar operands; every value stays bounded so that tolerances mean something."""
+    dims = ", ".join(str(d) for d in rows_shape)
+    reduced = ", ".join(str(d) for d in rows_shape[:-1] + (1,))
+    lines = [f"input x : f32[{dims}]", f"input col : f32[{reduced}]", f"input vec : f32[{rows_shape[-1]}]", "const k : f32[] = 0.75"]
+    full, per_row = ["x"], ["col"]
+    count = 0
+
+    def fresh():
+        nonlocal count
+        count += 1
+        return f"t{count}"
+
+    for _ in range(int(rng.integers(4, 10))):
+        kind = rng.choice(["unary", "binary", "reduce", "per_row"], p=[0.25, 0.35, 0.25, 0.15])
+        name = fresh()
+        if kind == "unary":
+            lines.append(f"{name} = {rng.choice(['tanh', 'sigmoid', 'relu', 'neg'])} {rng.choice(full)}")
+            full.append(name)
+        elif kind == "binary":
+            other = rng.choice(full + per_row + ["vec", "k"])
+            a, b = (rng.choice(full), other) if rng.random() < 0.5 else (other, rng.choice(full))
+            lines.append(f"{name} = {rng.choice(['add', 'sub', 'mul'])} {a}, {b}")
+            full.append(name)
+        elif kind == "reduce":
+            lines.append(f"{name} = {rng.choice(['row_sum', 'row_max'])} {rng.choice(full)}")
+            if lines[-1].split()[2] == "row_sum":  # keep magnitudes bounded: scale the sum by 1 / width
+                scaled = fresh()
+                lines.append(f"const inv{scaled} : f32[] = {1.0 / rows_shape[-1]!r}")
+                lines.append(f"{scaled} = mul {name}, inv{scaled}")
+                name = scaled
+            per_row.append(name)
+        else:
+            lines.append(f"{name} = {rng.choice(['add', 'mul', 'sub'])} {rng.choice(per_row)}, {rng.choice(per_row + ['k'])}")
+            per_row.append(name)
+    outputs = [full[-1]] + ([per_row[-1]] if len(per_row) > 1 else [])
+    if len(full) > 3 and rng.random() < 0.5:
+        outputs.append(full[len(full) // 2])
+    lines.append("output " + ", ".join(dict.fromkeys(outputs)))
+    return "\n".join(lines)
+
+
+def test_random_row_graphs_fused_and_separate_agree(mc, oracle):
+    """40 random row graphs: the default lowering (row kernels, recomputation) gives the bits of the plain per-step
+    lowering, and both are within the elementwise tolerance of the double-precision oracle."""
+    rng = np.random.default_rng(2024)
+    fused_seen = 0
+    for case in range(40):
+        shape = [(7, 1536), (3, 5, 1100), (64, 96), (5, 9000), (2, 3, 33), (16, 1024)][case % 6]
+        text = _random_row_graph(rng, shape)
+        g, ins = oracle_inputs(oracle, text, seed=case + 1, lo=-1.0, hi=1.0)
+        want = oracle.evaluate_f64(g, ins)
+        with mc.CompiledGraph(text=text) as exe:
+            got = exe.run(ins)
+            fused_seen += "mc_row_fused" in exe.kernel_sources
+        with mc.CompiledGraph(text=text, options={"fuse_rows": 0, "rematerialize": 0}) as exe:
+            plain = exe.run(ins)
+        for a, b, w in zip(got, plain, want):
+            assert np.array_equal(a, b), f"case {case}:\n{text}"
+            ok, msg = all_close(a, w, 2e-5, 2e-6)
+            assert ok, f"case {case}: {msg}\n{text}"
+    assert fused_seen >= 20
