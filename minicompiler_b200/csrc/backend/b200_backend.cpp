@@ -245,11 +245,26 @@ private:
     // Applies when every tensor the kernels walk has the same element count (pipeline_elements_).
     Status run_pipelined(const std::vector<const float*>& inputs, const std::vector<float*>& outputs) {
         const std::size_t total = pipeline_elements_;
-        const std::size_t slices = kPipelineSlices;
+        const std::size_t slices = pipeline_slices();
         const std::size_t per = ((total + slices - 1) / slices + 1023) / 1024 * 1024;  // whole 128-bit groups, whole periods
-        for (std::size_t c = 0; c * per < total; ++c) {
-            const std::size_t first = c * per;
-            const std::size_t count = std::min(per, total - first);
+        // Equal slices, except that the first and the last are cut further (1/4, 1/4, 1/2 and back): the bus is idle in
+        // one direction while the first slice comes in and while the last goes out, so those are kept short.
+        std::vector<std::size_t> counts;
+        for (std::size_t first = 0; first < total; first += per) {
+            const std::size_t n = std::min(per, total - first);
+            const std::size_t quarter = n / 4 / 1024 * 1024;
+            const bool head = first == 0, tail = first + per >= total;
+            if (quarter == 0 || (!head && !tail) || (head && tail)) {
+                counts.push_back(n);
+            } else if (head) {
+                counts.insert(counts.end(), {quarter, quarter, n - 2 * quarter});
+            } else {
+                counts.insert(counts.end(), {n - 2 * quarter, quarter, quarter});
+            }
+        }
+        std::size_t first = 0;
+        for (std::size_t c = 0; c < counts.size(); first += counts[c], ++c) {
+            const std::size_t count = counts[c];
             for (std::size_t k = 0; k < inputs.size(); ++k) {
                 const NodeId id = graph_.inputs()[k];
                 const std::size_t n = graph_.node(id).type.num_elements();
@@ -499,9 +514,9 @@ private:
         if (pipeline_elements_ > 0) {
             MCD_TRY(mcd_stream_create(&copy_in_));
             MCD_TRY(mcd_stream_create(&copy_out_));
-            slice_in_.assign(kPipelineSlices, nullptr);
-            slice_done_.assign(kPipelineSlices, nullptr);
-            for (std::size_t c = 0; c < kPipelineSlices; ++c) {
+            slice_in_.assign(pipeline_slices() + 4, nullptr);  // the first and the last slice are cut in three
+            slice_done_.assign(pipeline_slices() + 4, nullptr);
+            for (std::size_t c = 0; c < slice_in_.size(); ++c) {
                 MCD_TRY(mcd_event_create(&slice_in_[c]));
                 MCD_TRY(mcd_event_create(&slice_done_[c]));
             }
@@ -737,7 +752,9 @@ private:
     void* arena_ = nullptr;
     void* replay_ = nullptr;
     bool streams_only_ = false;
-    static constexpr std::size_t kPipelineSlices = 48;
+    std::size_t pipeline_slices() const {
+        return static_cast<std::size_t>(std::min(256, std::max(2, options_.host_io_slices)));
+    }
     std::size_t pipeline_elements_ = 0;
     void* copy_in_ = nullptr;
     void* copy_out_ = nullptr;

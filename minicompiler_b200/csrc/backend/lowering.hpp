@@ -83,6 +83,7 @@ struct CudaOptions {
     // 256-thread blocks with four 128-bit loads in flight per thread stream faster than eight (6.1 vs
     // 5.5 TB/s on the 512 MiB GELU pass): more outstanding requests than that only queue up in front of HBM.
     int eltwise_blocks_per_sm = 4;
+    int host_io_slices = 10;    // slices of the pipelined run() on pinned host memory (host_io = 1)
     bool fuse_rows = true;      // runs of steps on rows of one shape become one kernel (reduce_codegen.hpp)
     bool rematerialize = true;  // recompute cheap elementwise values read by a row reduction in each reader
 };

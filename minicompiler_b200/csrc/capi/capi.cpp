@@ -115,6 +115,8 @@ Status parse_options(const char* text, cuda::CudaOptions* options) {
                 options->streaming_hints = number != 0;
             } else if (key == "gemm_variant") {
                 options->gemm_variant = static_cast<int>(number);
+            } else if (key == "host_io_slices") {
+                options->host_io_slices = static_cast<int>(number);
             } else if (key == "fuse_rows") {
                 options->fuse_rows = number != 0;
             } else if (key == "rematerialize") {
@@ -129,7 +131,7 @@ Status parse_options(const char* text, cuda::CudaOptions* options) {
                 options->eltwise_blocks_per_sm = static_cast<int>(number);
             } else {
                 return Error{"unknown option '" + key +
-                             "' (device, matmul, vectorize, fuse_epilogue, b_layout, unroll, streaming, gemm_variant, fmad, blocks_per_sm, graph, host_io, rematerialize, fuse_rows)"};
+                             "' (device, matmul, vectorize, fuse_epilogue, b_layout, unroll, streaming, gemm_variant, fmad, blocks_per_sm, graph, host_io, host_io_slices, rematerialize, fuse_rows)"};
             }
         }
     }
