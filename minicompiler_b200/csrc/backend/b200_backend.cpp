@@ -569,10 +569,12 @@ private:
         int blocks_per_sm = 0;
         MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(kElementwiseBlock), 0, &blocks_per_sm));
         if (options_.eltwise_blocks_per_sm > 0) blocks_per_sm = std::min(blocks_per_sm, options_.eltwise_blocks_per_sm);
-        // One wave of resident blocks at most; the tile loop inside the kernel covers the rest.
+        // By default one block per tile of the tensor (measured on B200: 6.32 against 5.94 TB/s for one wave of
+        // resident blocks that loop); a positive blocks_per_sm asks for the looping form with that many blocks per SM.
         const std::size_t per_block = static_cast<std::size_t>(kElementwiseBlock) * kernel.unroll;
         const std::size_t wanted = (launch->count + per_block - 1) / per_block;
-        const std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
+        std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
+        if (options_.eltwise_blocks_per_sm <= 0) resident = wanted;
         launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(wanted, resident)));
         launch->vectorized = kernel.vectorized;
         if (kernel.has_f32_out) {
@@ -615,7 +617,8 @@ private:
         int blocks_per_sm = 0;
         MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(kernel.block), 0, &blocks_per_sm));
         const std::size_t wanted = (rows + kernel.rows_per_block - 1) / kernel.rows_per_block;
-        const std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
+        std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
+        if (options_.eltwise_blocks_per_sm <= 0) resident = wanted;
         launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(wanted, resident)));
         launch->pointers.push_back(address(step.result, kRepF32));
         launch->advances.push_back(0);
@@ -646,9 +649,10 @@ private:
         launch->block = row_block(step.reduce_shape.back());
         int blocks_per_sm = 0;
         MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(launch->block), 0, &blocks_per_sm));
-        const std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
+        std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
         const std::size_t rows_per_block = launch->block / row_threads(step.reduce_shape.back());
         const std::size_t wanted = (rows + rows_per_block - 1) / rows_per_block;
+        if (options_.eltwise_blocks_per_sm <= 0) resident = wanted;
         launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(wanted, resident)));
         for (NodeId w : step.row_outputs) {
             launch->pointers.push_back(address(w, kRepF32));

@@ -79,10 +79,10 @@ struct CudaOptions {
     // 2 = kernels on host memory in place only.
     int host_io = 1;
     bool eltwise_fmad = false;      // let the compiler contract a*b+c in generated kernels (not bit-exact vs the CPU)
-    // Cap on resident blocks per SM for the one-wave grid (0 = whatever occupancy allows). On B200 four
-    // 256-thread blocks with four 128-bit loads in flight per thread stream faster than eight (6.1 vs
-    // 5.5 TB/s on the 512 MiB GELU pass): more outstanding requests than that only queue up in front of HBM.
-    int eltwise_blocks_per_sm = 4;
+    // Grid of the generated kernels. 0 (default): one block per tile of the tensor (per row, or 8 rows, for the row
+    // kernels) - on B200 the 512 MiB GELU pass streams at 6.32 TB/s this way. n > 0: one wave of n looping blocks per
+    // SM instead (4 was the best of those at 5.94 TB/s; 3 gives 5.43, 5 gives 5.46, 8 gives 5.36).
+    int eltwise_blocks_per_sm = 0;
     int host_io_slices = 10;    // slices of the pipelined run() on pinned host memory (host_io = 1)
     bool fuse_rows = true;      // runs of steps on rows of one shape become one kernel (reduce_codegen.hpp)
     bool rematerialize = true;  // recompute cheap elementwise values read by a row reduction in each reader
