@@ -32,7 +32,9 @@ __device__ __forceinline__ void mc_gemm_f32_body(const float* __restrict__ A, co
     const int k_end = min(K, k_begin + k_per_split);
 
     // Global -> register staging coordinates.
-    const int a_row = tid >> 2;        // 0..63 (and +64)
+    // 0..63 (and +64). The two upper k-groups of a lane quad take the row 8 further on, so that the transposed
+    // stores of a warp (k-groups 16 banks apart at pitch 132) fall on 32 different banks.
+    const int a_row = (tid >> 2) ^ ((tid & 2) << 2);
     const int a_k = (tid & 3) << 2;    // 0,4,8,12
     const int b_k = tid >> 5;          // 0..7 (and +8)
     const int b_n = (tid & 31) << 2;   // 0..124
