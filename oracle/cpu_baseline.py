@@ -57,7 +57,13 @@ def _load() -> C.CDLL:
 
 
 def max_threads() -> int:
-    return int(_load().oracle_max_threads())
+    """Host threads the port may use: the cores this process may run on. The OpenMP default is not used because
+    launchers such as torchrun export OMP_NUM_THREADS=1 to every rank; the kernels take the count explicitly."""
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    return max(1, min(cores, 64))
 
 
 def _fptr(a: np.ndarray):
