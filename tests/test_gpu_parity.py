@@ -610,3 +610,22 @@ def test_random_row_graphs_fused_and_separate_agree(mc, oracle):
             ok, msg = all_close(a, w, 2e-5, 2e-6)
             assert ok, f"case {case}: {msg}\n{text}"
     assert fused_seen >= 20
+
+
+@pytest.mark.parametrize("matmul,tol", [("auto", 1e-4), ("tensor_core_bf16", 2e-2), ("tensor_core_tf32", 5e-3)])
+def test_attention_like_graph_mixes_matmuls_and_a_row_kernel(mc, oracle, matmul, tol):
+    """scores = q k^T (given as k_t), softmax over rows in one row kernel, out = p v: the row kernel reads a matmul
+    result and feeds the next matmul, which for the 16-bit kernel needs its operand recast after the row kernel."""
+    text = ("input q : f32[192, 64]\ninput kt : f32[64, 1280]\ninput v : f32[1280, 96]\nconst scale : f32[] = 0.125\n"
+            "s = matmul q, kt\nt = mul s, scale\nm = row_max t\nd = sub t, m\ne = exp d\nz = row_sum e\np = div e, z\n"
+            "o = matmul p, v\noutput o, z")
+    g, ins = oracle_inputs(oracle, text, seed=21, lo=-1.0, hi=1.0)
+    want = oracle.evaluate_f64(g, ins)
+    with mc.CompiledGraph(text=text, options={"matmul": matmul}) as exe:
+        got = exe.run(ins)
+        assert "mc_row_fused" in exe.kernel_sources
+    with mc.CompiledGraph(text=text, options={"matmul": matmul, "fuse_rows": 0, "rematerialize": 0}) as exe:
+        plain = exe.run(ins)
+    for a, b, w in zip(got, plain, want):
+        assert np.array_equal(a, b)
+        assert norm_scaled_error(a, w) <= tol, f"{matmul}: {norm_scaled_error(a, w):.2e}"
