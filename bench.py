@@ -3,16 +3,25 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
 One "step" is one execution of a compiled graph (`mc_enqueue`) on inputs already resident in HBM.
-The default workload is the headline memory-bound config: the tanh-GELU chain on f32[8192,8192]
-(one fused kernel; 536,870,912 algorithmic bytes per step), reported as fused-eltwise HBM GB/s.
-Other workloads (`--workload`): c1, c3_fp32, c3_tf32, c4_bf16, c4_f16, c4_tf32, c4_fp32, c5_f16, c5_bf16
-report graph TFLOP/s; x1_softmax and x2_layernorm (extension graphs) report GB/s of read-x-plus-write-y bytes. With N > 1 (launched by torchrun, one rank per GPU) c2/c4 run one replica per
-GPU on rank-specific data (weak scaling) and c5/c3/c1 shard their batch dim over the ranks.
+The default workload is the batch-sharded 8-layer MLP stack in FP16 tensor-core arithmetic
+(x[65536,2048], eight 2048x2048 layers with a folded BatchNorm affine and relu in each GEMM's
+epilogue: 8 launches, 4.4 TFLOP per step), reported as graph TFLOP/s. With N > 1 (launched by
+torchrun, one rank per GPU) its batch dim is sharded over the ranks (strong scaling), and so are
+c3/c1; c2/c4 run one replica per GPU on rank-specific data (weak scaling).
+At N = 1 the same JSON line carries an `also` list with brief measurements of the other configs
+(`--also none` turns it off): c2 (tanh-GELU chain, fused-eltwise HBM GB/s), c4 shapes of the
+tensor-core sweep, c3 in TF32 and FP32, c1.
+Other workloads (`--workload`): c1, c2, c3_fp32, c3_tf32, c4_bf16, c4_f16, c4_tf32, c4_fp32, c5_f16,
+c5_bf16, the rest of the c4 sweep (c4_<fmt>_<size>|m16|m128|tallk); x1_softmax and x2_layernorm
+(extension graphs) report GB/s of read-x-plus-write-y bytes.
 
 Rank 0 prints ONE JSON line. `value` is device-timed with CUDA events on the launching stream,
 max over ranks; `e2e` is the same metric through `mc_run` on pinned host buffers (copies inside
 the timed region); `roofline` relates the dominant kernel to the measured peak in
-MEASURED_PEAKS.json; `cpu_baseline` times the CPU oracle on a bounded sample.
+MEASURED_PEAKS.json; `cpu_baseline` times the CPU oracle on a bounded sample, on all host threads
+and on one thread (the reference's own CPU configuration, bench/harness.hpp:254).
+Inputs are seeded synthetic tensors with the configs' shapes and distributions (numpy's PCG64
+generator: the bench never compares values, the parity tests do, on the oracle's own stream).
 
 `--impl reference` times the reference's CPU path instead: the Eigen backend cannot be built
 here (Eigen 3.4.0 is not vendored and not installed), so it is the oracle port, on host cores.
@@ -131,17 +140,35 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def make_inputs(oracle, graph, dist, seed):
+def make_inputs(graph, dist, seed):
+    """Seeded synthetic inputs of the workload's shapes and distribution (N(0,1) or uniform(-1,1)), float32.
+    numpy's PCG64 generator: a 65536 x 2048 tensor takes about a second, where the oracle's scalar splitmix64
+    stream (the one the parity tests feed to GPU and oracle alike) takes most of a minute."""
     ins = []
     for k, name in enumerate(graph.inputs):
         shape = graph.node(name).shape
         n = int(np.prod(shape))
-        v = oracle.normal_values(n, seed + k) if dist == "normal" else oracle.uniform_values(n, seed + k, -1.0, 1.0)
+        rng = np.random.default_rng(seed + k)
+        if dist == "normal":
+            v = rng.standard_normal(n, dtype=np.float32)
+        else:
+            v = rng.random(n, dtype=np.float32)
+            v *= 2.0
+            v -= 1.0
         ins.append(v.reshape(shape))
     return ins
 
 
-def cpu_sample(oracle, path, dims, batch_dim, kind, dist, rows_cap):
+def workload_config(workload, dims):
+    """The `config` object both arms print for a workload."""
+    name, _, matmul, batch_dim, kind, dist = WORKLOADS[workload]
+    return {"workload": workload, "graph": name, "dims": dims, "matmul": matmul, "sharded_dim": batch_dim,
+            "inputs": f"{dist}, seeded (numpy PCG64, seed 1 + 1000*rank)",
+            "l2": "a step whose arena is below 256 MiB is timed on its own after a 256 MiB overwrite that flushes L2; "
+                  "larger steps stream more than the 126 MB L2 holds and run back to back"}
+
+
+def cpu_sample(oracle, path, dims, batch_dim, kind, dist, rows_cap, threads=None):
     """The CPU port (oracle/cpu_baseline.py over oracle_kernels.c) prepared on a row sample of the workload."""
     from oracle import cpu_baseline
 
@@ -152,15 +179,15 @@ def cpu_sample(oracle, path, dims, batch_dim, kind, dist, rows_cap):
     if lead:
         sample_dims[lead] = rows
     g = oracle.parse_mcg_file(path, sample_dims)
-    threads = cpu_baseline.max_threads()
-    plan = cpu_baseline.CpuPlan(g, threads)
-    ins = make_inputs(oracle, g, dist, 1)
+    plan = cpu_baseline.CpuPlan(g, threads or cpu_baseline.max_threads())
+    ins = make_inputs(g, dist, 1)
     return plan, ins, algorithmic_work(oracle, g, kind), plan.threads, f"{rows} of {rows_full} rows of '{lead}'"
 
 
-def cpu_sample_rate(oracle, path, dims, batch_dim, kind, dist, seconds_target=10.0):
+def cpu_sample_rate(oracle, path, dims, batch_dim, kind, dist, seconds_target=10.0, threads=None, rows_cap=None):
     """Times the CPU port on a bounded sample; returns (rate, threads, description)."""
-    plan, ins, work, threads, what = cpu_sample(oracle, path, dims, batch_dim, kind, dist, 2048 if kind == "bytes" else 1024)
+    cap = rows_cap or (2048 if kind == "bytes" else 1024)
+    plan, ins, work, threads, what = cpu_sample(oracle, path, dims, batch_dim, kind, dist, cap, threads)
     plan.run(ins)  # warm
     t0, reps = time.perf_counter(), 0
     while True:
@@ -194,10 +221,11 @@ def run_reference_arm(args):
     line = {
         "impl": "reference", "metric": "fused-eltwise HBM GB/s" if kind == "bytes" else "graph TFLOP/s", "value": value, "unit": unit,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "graph": name, "dims": dims,
-                   "note": "reference CPU path = C port of its CPU kernels (Eigen 3.4.0 is absent, so the reference's own CPU "
-                           f"backend cannot be built); each step runs {what}"},
+        "higher_is_better": True, "scaling": "strong" if batch_dim is not None and args.gpus > 1 else "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.workload, dims),
+        "note": "reference CPU path = C port of its CPU kernels in FP32 (Eigen 3.4.0 is absent, so the reference's own CPU "
+                f"backend cannot be built); each step runs {what}",
         "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "port", "sample": f"{what} per step"},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -205,20 +233,29 @@ def run_reference_arm(args):
     print(json.dumps(line))
 
 
+DEFAULT_ALSO = "c2,c4_bf16,c4_bf16_16384,c4_bf16_m128,c3_tf32,c3_fp32,c1"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
-    ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="c5_f16", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--also", default="", help="comma-separated extra workloads measured briefly (N=1 only)")
+    ap.add_argument("--also", default=None,
+                    help="comma-separated extra workloads measured briefly (N=1 only); default: "
+                         f"{DEFAULT_ALSO} beside the default workload, nothing beside any other; 'none' turns it off")
     ap.add_argument("--options", default="", help="extra compile options, e.g. gemm_variant=2,fuse_epilogue=0 (for A/B measurements)")
     ap.add_argument("--dims", default="", help="override dims of the workload, e.g. M=4096,N=8192 (for small profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.also is None:
+        args.also = DEFAULT_ALSO if (args.workload == "c5_f16" and not args.dims and not args.options) else ""
+    if args.also == "none":
+        args.also = ""
 
     if args.impl == "reference":
         run_reference_arm(args)
@@ -266,8 +303,9 @@ def main():
                 exe.refresh_constants()
         g = oracle.parse_mcg_file(path, my_dims)
         work_rank = algorithmic_work(oracle, g, kind)
-        ins = make_inputs(oracle, g, dist_name, 1 + 1000 * rank)
+        ins = make_inputs(g, dist_name, 1 + 1000 * rank)
         pinned_in = [torch.from_numpy(a.reshape(-1)).pin_memory() for a in ins]
+        del ins
         pinned_out = [torch.empty(n, dtype=torch.float32).pin_memory() for n in exe.output_elements]
         exe.upload([t.numpy() for t in pinned_in])
         # A stream of our own: torch's default stream has handle 0, which mc_enqueue reads as "the executable's
@@ -343,9 +381,10 @@ def main():
             e2e = {"value": work_all * e2e_steps / float(tt.item()) / denom, "unit": "GB/s" if kind == "bytes" else "TFLOP/s",
                    "h2d_bytes_per_step": int(sum(a.numel() * 4 for a in pinned_in)),
                    "d2h_bytes_per_step": int(sum(a.numel() * 4 for a in pinned_out)), "steps": e2e_steps,
+                   "ms_per_step": float(tt.item()) / e2e_steps * 1e3,
                    "timing": "host wall clock around mc_run (it synchronizes), max over ranks",
-                   "path": "mc_run on pinned host buffers; a graph that is one streaming elementwise launch is cut into slices "
-                           "whose H2D copy, kernel and D2H copy overlap on three streams, any other graph is copied in, run and "
+                   "path": "mc_run on pinned host buffers: a graph whose rows are independent is cut into row slices whose "
+                           "H2D copy, kernels and D2H copy overlap on three streams; any other graph is copied in, run and "
                            "copied out"}
 
         peaks = measured_peaks()
@@ -354,12 +393,15 @@ def main():
         if kind == "bytes":
             achieved = work_rank / (avg_ms * 1e-3) / 1e9
             peak, unit, bound = peaks["hbm_gbs"], "GB/s", "hbm"
+            peak_kind = "copy bandwidth"
         else:
             achieved = work_rank / (avg_ms * 1e-3) / 1e12
             sustained = total_ms > 1000.0
             base = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
             peak = {"f32": 2 * 148 * 128 * 1.965e9 / 1e12, "tf32": base / 2.0}.get(DTYPES[matmul], base)
             unit, bound = "TFLOP/s", "tensor" if matmul != "auto" else "fp32-fma"
+            peak_kind = ("FP32 FMA peak at the maximum SM clock (2 x 148 SMs x 128 lanes x 1965 MHz)" if matmul == "auto" else
+                         ("sustained" if sustained else "burst") + " cuBLAS bf16 GEMM" + (", halved for TF32" if DTYPES[matmul] == "tf32" else ""))
         traffic = None
         tfile = ROOT / "profiles" / "ncu_traffic.json"
         if tfile.exists():
@@ -368,28 +410,33 @@ def main():
             except Exception:
                 traffic = None
         roofline = {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-                    "traffic": traffic, "peak_source": f"of {peaks['source']}", "kernel_ms_avg": avg_ms, "kernel_ms_median": median_ms,
-                    "algorithmic_per_launch": work_rank}
+                    "traffic": traffic, "peak_source": f"of {peaks['source']}: {peak_kind}",
+                    "kernel_ms_avg": avg_ms / max(1, launches_per_step), "step_ms_median": median_ms,
+                    "launches_per_step": launches_per_step, "algorithmic_per_launch": work_rank / max(1, launches_per_step),
+                    "kernels": exe.matmul_kernels if kind == "flops" else ["mc_elementwise (generated)"]}
 
         cpu = None
         if with_cpu and rank == 0:
             rate, threads, sample = cpu_sample_rate(oracle, path, dims, batch_dim, kind, dist_name)
-            cpu = {"value": rate, "unit": "GB/s" if kind == "bytes" else "TFLOP/s", "cores": threads, "kind": "port", "sample": sample}
+            one_rate, _, one_sample = cpu_sample_rate(oracle, path, dims, batch_dim, kind, dist_name, seconds_target=6.0, threads=1,
+                                                      rows_cap=512 if kind == "bytes" else 128)
+            cpu = {"value": rate, "unit": "GB/s" if kind == "bytes" else "TFLOP/s", "cores": threads, "kind": "port", "sample": sample,
+                   "one_thread": {"value": one_rate, "cores": 1, "sample": one_sample,
+                                  "note": "the reference's own CPU configuration is single-threaded (bench/harness.hpp:254)"}}
 
         result = {
             "metric": "fused-eltwise HBM GB/s" if kind == "bytes" else "graph TFLOP/s", "value": value,
             "unit": "GB/s" if kind == "bytes" else "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": avg_ms, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": DTYPES[matmul], "data": "synthetic",
-            "config": {"workload": workload, "graph": name, "dims": dims, "per_rank_dims": my_dims, "matmul": matmul,
-                       "matmul_kernels": exe.matmul_kernels, "kernel_launches_per_step": launches_per_step,
-                       "l2": "flushed between steps (256 MiB overwrite), steps timed one by one" if flush_l2
-                       else "not flushed: the tensors a step streams exceed the 126 MB L2",
-                       "inputs": f"{dist_name} (splitmix64 stream, seed 1 + 1000*rank)"},
+            "config": workload_config(workload, dims),
+            "per_rank_dims": my_dims, "matmul_kernels": exe.matmul_kernels, "kernel_launches_per_step": launches_per_step,
+            "l2_flushed_between_steps": flush_l2,
             "e2e": e2e, "gpu_launches": int(count1 - count0), "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
             "jit_compile_ms": exe.jit_compile_ms, "arena_bytes": exe.arena_bytes,
         }
         exe.release()
+        del pinned_in, pinned_out
         return result
 
     line = measure(args.workload, args.steps, args.warmup, not args.no_e2e, not args.no_cpu_baseline)
@@ -398,8 +445,8 @@ def main():
         for wl in [w for w in args.also.split(",") if w]:
             try:
                 r = measure(wl, max(5, min(args.steps, 20)), 3, False, False)
-                extra.append({k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "dtype", "roofline", "gpu_launches")}
-                             | {"workload": wl, "matmul_kernels": r["config"]["matmul_kernels"]})
+                extra.append({k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "dtype", "roofline", "gpu_launches",
+                                                "matmul_kernels", "clocks")} | {"workload": wl, "dims": r["config"]["dims"]})
             except Exception as e:  # an extra must never lose the headline line
                 extra.append({"workload": wl, "error": str(e)[:300]})
         line["also"] = extra

@@ -82,6 +82,11 @@ MC_EXPORT const char* mc_last_error(void);
  * replicate them; after overwriting the range call mc_refresh_constants. */
 MC_EXPORT int mc_constants_region(void* handle, void** device_ptr, size_t* bytes);
 MC_EXPORT int mc_refresh_constants(void* handle);
+/* Device address of the 32-bit status word of a compiled graph, or NULL in *device_ptr when none of its
+ * kernels can wait. A tensor-core matmul that gives up a bounded wait ORs a code into it; mc_synchronize and
+ * mc_download then fail with a message and clear it. Exposed so that this error path can be exercised from
+ * the host (write a non-zero value with mcd_copy_h2d) without making any kernel wait. */
+MC_EXPORT int mc_status_word_ptr(void* handle, void** device_ptr);
 /* Device address of input / output k (float32, dense, graph layout). */
 MC_EXPORT int mc_input_device_ptr(void* handle, int k, void** device_ptr, size_t* elements);
 MC_EXPORT int mc_output_device_ptr(void* handle, int k, void** device_ptr, size_t* elements);
@@ -124,6 +129,9 @@ MC_EXPORT int mcb_graph_check_kernels(const void* graph, const char* options, in
  * reference and prints one kernel per graph node (tools/mcc.cpp:200-210), this is what actually runs. */
 MC_EXPORT int mcb_graph_plan_sources(const void* graph, const char* options, int sm_count, char* out, int size);
 
+/* 1 when kernels may read and write `count` caller buffers in place (mc_run on pinned memory): vectorised kernels
+ * move 128 bits per access, so every buffer must start on a 16-byte boundary; otherwise mc_run stages copies. */
+MC_EXPORT int mcb_in_place_pointers_ok(const void* const* pointers, int count, int any_vectorized);
 MC_EXPORT void mcb_uniform_values(float* out, long long count, unsigned long long seed, float lo, float hi);
 MC_EXPORT int mcb_split_k_splits(int m, int n, int k, int sm_count, int blocks_per_sm);
 MC_EXPORT int mcb_tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes);

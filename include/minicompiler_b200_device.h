@@ -78,10 +78,16 @@ MCD_API int mcd_event_elapsed_ms(void* start, void* stop, float* ms); /* waits f
  * (src/cuda/kernel_compiler.cpp:24-57, src/cuda/cuda_backend.cpp:174-175,
  * :311-317). Compiles CUDA C++ to an sm_100a cubin with NVRTC and loads it
  * into `device`'s primary context; results are cached process-wide, keyed by
- * (device, options, source, kernel name), so a kernel is never launched on a
- * device other than the one its module was loaded for. */
+ * (device, options, hash of the source, kernel name), so a kernel is never
+ * launched on a device other than the one its module was loaded for. NVRTC
+ * runs outside the cache's lock. Each successful call takes one reference. */
 MCD_API int mcd_jit_kernel(int device, const char* source, const char* kernel_name, const char* options,
                            void** function, double* compile_ms);
+/* Gives back one reference taken by mcd_jit_kernel. A kernel nobody holds stays loaded while few such
+ * kernels exist and is unloaded, least recently used first, beyond that; never launch it after the release. */
+MCD_API int mcd_jit_release(void* function);
+/* Loaded modules, and how many of them nobody holds (for tests and leak hunting). */
+MCD_API int mcd_jit_cache_stats(long long* modules, long long* idle);
 MCD_API int mcd_jit_occupancy(void* function, int block_threads, size_t dynamic_smem, int* blocks_per_sm);
 MCD_API int mcd_jit_set_dynamic_smem(void* function, size_t bytes);
 MCD_API int mcd_launch(void* function, unsigned grid_x, unsigned grid_y, unsigned grid_z, unsigned block_x,
@@ -174,11 +180,15 @@ MCD_API const char* mcd_gemm_source(int arith);
 MCD_API const char* mcd_gemm_entry_point(const mcd_gemm_args* args);
 /* Dynamic shared memory the entry point needs (set it with mcd_jit_set_dynamic_smem). */
 MCD_API size_t mcd_gemm_dynamic_smem(int arith);
+/* Host-only check of the bookkeeping behind per-device kernel set-up (the opt-in to large dynamic shared
+ * memory is kept per device): for a sequence of device ordinals, first[i] = 1 where a launch on
+ * devices[i] would run the set-up, 0 where it was done by an earlier element. Touches no GPU. */
+MCD_API int mcd_per_device_once_probe(const int* devices, int count, int* first);
 /* Whether tcgen05 kernels can run on `device` (compute capability 10.x). */
 MCD_API int mcd_tensor_core_supported(int device, int arith);
 
-/* Bytes of built-in scratch behind mcd_gemm_f32_split_no_alloc (held by every GPU that loads
- * the library, until the process exits). */
+/* Bytes of built-in scratch behind mcd_gemm_f32_split_no_alloc (held, from the first call on it
+ * until the process exits, by every GPU the entry point is used on). */
 #define MCD_NO_ALLOC_SCRATCH_BYTES (16u << 20)
 
 /* FP32 split-K matmul that allocates nothing: C[m,n] = A[m,k] * B[k,n], all dense row-major
@@ -195,9 +205,12 @@ MCD_API int mcd_tensor_core_supported(int device, int arith);
  *   - all calls on one GPU share that array: two calls that overlap on the GPU (different
  *     streams) race on it. Calls on one stream are safe. Nothing in it needs clearing between
  *     calls, every partial sum is rewritten before it is read;
- *   - the first call on each GPU looks up the array's device address (cudaGetSymbolAddress) with
- *     that GPU current; make that first call before starting any stream capture.
- * It calls no cudaMalloc, cudaFree or allocating library routine. */
+ *   - the array comes into being on the first call per GPU: CUDA loads the module that owns it lazily, so
+ *     that one call (cudaGetSymbolAddress, with that GPU current) makes the driver set aside the 16 MiB and may
+ *     synchronise the device. Make it at start-up - a tiny problem with splits = 1 is enough - BEFORE the
+ *     caller's own pool takes the rest of HBM (afterwards it can fail with out-of-memory) and before any stream
+ *     capture. Every later call on that GPU allocates nothing and synchronises nothing.
+ * The entry point itself calls no cudaMalloc, cudaFree or allocating library routine. */
 MCD_API int mcd_gemm_f32_split_no_alloc(const float* a, const float* b, float* c, int m, int n, int k, int splits,
                                         void* stream);
 

@@ -58,6 +58,13 @@ def lib() -> C.CDLL:
         "mc_last_error": (cp, []),
         "mc_constants_region": (i32, [vp, C.POINTER(vp), C.POINTER(C.c_size_t)]),
         "mc_refresh_constants": (i32, [vp]),
+        "mc_status_word_ptr": (i32, [vp, C.POINTER(vp)]),
+        "mcb_in_place_pointers_ok": (i32, [C.POINTER(vp), i32, i32]),
+        "mcd_copy_h2d": (i32, [vp, vp, C.c_size_t, vp]),
+        "mcd_copy_d2h": (i32, [vp, vp, C.c_size_t, vp]),
+        "mcd_device_synchronize": (i32, []),
+        "mcd_jit_cache_stats": (i32, [C.POINTER(i64), C.POINTER(i64)]),
+        "mcd_per_device_once_probe": (i32, [C.POINTER(i32), i32, C.POINTER(i32)]),
         "mc_input_device_ptr": (i32, [vp, i32, C.POINTER(vp), C.POINTER(C.c_size_t)]),
         "mc_output_device_ptr": (i32, [vp, i32, C.POINTER(vp), C.POINTER(C.c_size_t)]),
         "mc_intermediate_bytes": (i64, [vp]),
@@ -269,6 +276,13 @@ class CompiledGraph:
     def refresh_constants(self) -> None:
         if lib().mc_refresh_constants(self._h) != 0:
             raise McError(_last_error())
+
+    def status_word_ptr(self) -> int:
+        """Device address of the status word (0 when no kernel of this graph can wait)."""
+        ptr = C.c_void_p()
+        if lib().mc_status_word_ptr(self._h, C.byref(ptr)) != 0:
+            raise McError("not a GPU executable")
+        return ptr.value or 0
 
     def input_device_ptr(self, k: int):
         ptr, n = C.c_void_p(), C.c_size_t()

@@ -3,6 +3,8 @@
 #include "minicompiler_b200_device.h"
 
 #include <algorithm>
+#include <cstdint>
+#include <cstdio>
 #include <cstring>
 
 namespace minicompiler {
@@ -65,6 +67,7 @@ public:
     ~B200Executable() override {
         if (arena_ != nullptr || stream_ != nullptr) mcd_set_device(options_.device);
         if (replay_ != nullptr) mcd_graph_destroy(replay_);
+        for (void* f : jit_functions_) mcd_jit_release(f);
         for (void* e : slice_in_) mcd_event_destroy(e);
         for (void* e : slice_done_) mcd_event_destroy(e);
         if (copy_in_ != nullptr) mcd_stream_destroy(copy_in_);
@@ -130,6 +133,9 @@ public:
     }
 
     Status enqueue(void* stream) override {
+        // One process may drive several GPUs: launches (and the tensor maps and per-device kernel set-up behind a
+        // matmul) belong to this executable's device whatever the calling thread used last.
+        MCD_TRY(mcd_set_device(options_.device));
         void* s = stream != nullptr ? stream : stream_;
         if (replay_ != nullptr) {
             MCD_TRY(mcd_graph_launch(replay_, s));
@@ -181,6 +187,8 @@ public:
         return Status();
     }
 
+    void* status_word_address() const override { return uses_status_ ? status_word() : nullptr; }
+
     std::size_t arena_bytes() const override { return arena_bytes_; }
     std::string plan_description() const override { return describe(graph_, lowered_); }
 
@@ -213,6 +221,14 @@ private:
         for (std::size_t k = 0; k < outputs.size(); ++k) {
             if (mcd_host_device_pointer(outputs[k], &out_alias[k]) != 0) return Status();
         }
+        // The generated kernels move 128 bits per access when they are vectorised, which the arena's 256-byte
+        // alignment guarantees but a caller's buffer (a view into a pinned allocation, say) may not: such a
+        // call takes the staged path, whose copies have no alignment requirement.
+        bool any_vectorized = false;
+        for (const std::unique_ptr<Launch>& l : launches_) any_vectorized = any_vectorized || l->vectorized;
+        std::vector<const void*> touched(in_alias.begin(), in_alias.end());
+        touched.insert(touched.end(), out_alias.begin(), out_alias.end());
+        if (pipeline_elements_ == 0 && !in_place_pointers_ok(any_vectorized, touched)) return Status();
         MCD_TRY(mcd_set_device(options_.device));
         if (pipeline_elements_ > 0) {
             MC_TRY(run_pipelined(inputs, outputs));
@@ -562,6 +578,7 @@ private:
             return Error{std::string("compiling the kernel of '") + node.name + "' failed: " + mcd_last_error()};
         }
         jit_ms_ += ms;
+        jit_functions_.push_back(launch->function);
         sources_.push_back(kernel.source);
 
         const std::size_t n = node.type.num_elements();
@@ -609,6 +626,7 @@ private:
             return Error{std::string("compiling the kernel of '") + node.name + "' failed: " + mcd_last_error()};
         }
         jit_ms_ += ms;
+        jit_functions_.push_back(launch->function);
         sources_.push_back(kernel.source);
 
         const std::size_t rows = node.type.num_elements();
@@ -643,6 +661,7 @@ private:
             return Error{std::string("compiling the row kernel of '") + graph_.node(step.result).name + "' failed: " + mcd_last_error()};
         }
         jit_ms_ += ms;
+        jit_functions_.push_back(launch->function);
         sources_.push_back(source);
         const std::size_t rows = num_elements(step.reduce_shape) / static_cast<std::size_t>(step.reduce_shape.back());
         launch->count = static_cast<unsigned>(rows);
@@ -727,6 +746,7 @@ private:
                     return Error{std::string("compiling the epilogue of '") + graph_.node(step.result).name +
                                  "' failed: " + mcd_last_error()};
                 }
+                jit_functions_.push_back(g.reduce_function);
             } else {
                 // Only the entry point this launch uses is compiled out of the kernel family's text.
                 const std::string entry = mcd_gemm_entry_point(&g);
@@ -737,6 +757,7 @@ private:
                     return Error{std::string("compiling the epilogue of '") + graph_.node(step.result).name +
                                  "' failed: " + mcd_last_error()};
                 }
+                jit_functions_.push_back(g.function);
                 const std::size_t smem = mcd_gemm_dynamic_smem(g.arith);
                 if (smem > 0) MCD_TRY(mcd_jit_set_dynamic_smem(g.function, smem));
             }
@@ -773,6 +794,7 @@ private:
     std::vector<Launch> upload_recasts_;
     std::vector<Launch> constant_recasts_;
     std::vector<std::string> sources_;
+    std::vector<void*> jit_functions_;  // one reference each in the device layer's kernel cache
     double jit_ms_ = 0.0;
 };
 
@@ -812,6 +834,14 @@ Result<DeviceInfo> query_device(int device) {
 }
 
 double current_sm_clock_mhz(int device) { return mcd_current_sm_clock_mhz(device); }
+
+bool in_place_pointers_ok(bool any_vectorized, const std::vector<const void*>& pointers) {
+    if (!any_vectorized) return true;
+    for (const void* p : pointers) {
+        if (reinterpret_cast<std::uintptr_t>(p) % 16 != 0) return false;
+    }
+    return true;
+}
 
 Result<std::unique_ptr<CudaExecutable>> compile_for_cuda(const Graph& graph, const CudaOptions& options) {
     MC_TRY(graph.verify());

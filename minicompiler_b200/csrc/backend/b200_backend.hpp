@@ -87,12 +87,19 @@ public:
     // Re-derives the 16-bit / transposed forms of the constants from their FP32 form
     // (after the region was overwritten, e.g. by a broadcast).
     virtual Status refresh_constants() = 0;
+    // Device address of the word into which a tensor-core kernel that gives up a bounded wait ORs its code
+    // (nullptr when no launch of this executable can wait). synchronize() / download_outputs() read and clear it.
+    virtual void* status_word_address() const = 0;
     virtual std::size_t arena_bytes() const = 0;
     virtual std::string plan_description() const = 0;
     // Device address and element count of output k's FP32 buffer.
     virtual void output_buffer(std::size_t k, void** ptr, std::size_t* elements) const = 0;
     virtual void input_buffer(std::size_t k, void** ptr, std::size_t* elements) const = 0;
 };
+
+// Whether kernels may read and write these caller buffers in place: a vectorised kernel moves 128 bits per
+// access, so every buffer must then start on a 16-byte boundary (a pinned allocation does; a view into one need not).
+bool in_place_pointers_ok(bool any_vectorized, const std::vector<const void*>& pointers);
 
 Result<std::unique_ptr<CudaExecutable>> compile_for_cuda(const Graph& graph, const CudaOptions& options = {});
 Result<std::unique_ptr<Backend>> make_cuda_backend(const CudaOptions& options = {});

@@ -625,6 +625,7 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
         out.pool_steps.push_back(std::move(ps));
     }
     out.pool = plan_pool(out.pool_values, out.pool_steps);
+
     return out;
 }
 

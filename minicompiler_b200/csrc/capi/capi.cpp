@@ -317,6 +317,18 @@ int mc_constants_region(void* handle, void** device_ptr, size_t* bytes) {
     return 0;
 }
 
+int mc_status_word_ptr(void* handle, void** device_ptr) {
+    Compiled* c = as_compiled(handle);
+    if (c->gpu == nullptr || device_ptr == nullptr) return 1;
+    *device_ptr = c->gpu->status_word_address();
+    return 0;
+}
+
+int mcb_in_place_pointers_ok(const void* const* pointers, int count, int any_vectorized) {
+    std::vector<const void*> list(pointers, pointers + (count > 0 ? count : 0));
+    return minicompiler::cuda::in_place_pointers_ok(any_vectorized != 0, list) ? 1 : 0;
+}
+
 int mc_refresh_constants(void* handle) {
     Compiled* c = as_compiled(handle);
     return c->gpu != nullptr ? failed(c->gpu->refresh_constants()) : 1;

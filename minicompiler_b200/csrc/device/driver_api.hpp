@@ -15,6 +15,7 @@ struct DriverApi {
     CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
     CUresult (*ModuleLoadData)(CUmodule*, const void*) = nullptr;
     CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+    CUresult (*ModuleUnload)(CUmodule) = nullptr;
     CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
                              void**, void**) = nullptr;
     CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;

@@ -73,6 +73,7 @@ const DriverApi* driver_api() {
         ok = resolve("cuGetErrorString", api.GetErrorString) && ok;
         ok = resolve("cuModuleLoadData", api.ModuleLoadData) && ok;
         ok = resolve("cuModuleGetFunction", api.ModuleGetFunction) && ok;
+        ok = resolve("cuModuleUnload", api.ModuleUnload) && ok;
         ok = resolve("cuLaunchKernel", api.LaunchKernel) && ok;
         ok = resolve("cuFuncSetAttribute", api.FuncSetAttribute) && ok;
         ok = resolve("cuOccupancyMaxActiveBlocksPerMultiprocessor", api.OccupancyMaxActiveBlocksPerMultiprocessor) && ok;
@@ -351,16 +352,76 @@ int mcd_event_elapsed_ms(void* start, void* stop, float* ms) {
 }
 
 // ------------------------------------------------------------------- JIT
+//
+// Modules are cached process-wide. The key is (device, options, entry point, 64-bit hash and length of the
+// source), so the table does not keep the source texts. Every mcd_jit_kernel call takes a reference that
+// mcd_jit_release gives back; a module nobody holds stays loaded as long as at most kJitIdleLimit such
+// modules exist (a graph compiled again shortly after its executable was destroyed costs nothing), beyond
+// that the least recently used idle module is unloaded. NVRTC runs outside the lock, so threads compiling
+// different kernels (or for different devices) do not wait for one another.
 
 namespace {
+
+struct JitKey {
+    int device;
+    std::string options;
+    std::string entry;
+    unsigned long long hash;
+    std::size_t length;
+    bool operator<(const JitKey& o) const {
+        return std::tie(device, hash, length, entry, options) < std::tie(o.device, o.hash, o.length, o.entry, o.options);
+    }
+};
 
 struct JitEntry {
     CUmodule module = nullptr;
     CUfunction function = nullptr;
+    long refs = 0;
+    unsigned long long last_use = 0;
 };
 
+constexpr std::size_t kJitIdleLimit = 128;
+
 std::mutex g_jit_mutex;
-std::map<std::tuple<int, std::string, std::string, std::string>, JitEntry> g_jit_cache;
+std::map<JitKey, JitEntry> g_jit_cache;
+std::map<void*, JitKey> g_jit_by_function;
+unsigned long long g_jit_clock = 0;
+
+unsigned long long fnv1a64(const char* text, std::size_t n) {
+    unsigned long long h = 1469598103934665603ull;
+    for (std::size_t i = 0; i < n; ++i) {
+        h ^= static_cast<unsigned char>(text[i]);
+        h *= 1099511628211ull;
+    }
+    return h;
+}
+
+void unload_on(int device, CUmodule module) {
+    const DriverApi* drv = driver_api();
+    if (drv == nullptr || module == nullptr) return;
+    int current = -1;
+    cudaGetDevice(&current);
+    if (current != device) cudaSetDevice(device);
+    drv->ModuleUnload(module);
+    if (current != device && current >= 0) cudaSetDevice(current);
+}
+
+// Called with the lock held: unloads least-recently-used idle modules beyond the limit.
+void evict_idle_locked() {
+    for (;;) {
+        std::size_t idle = 0;
+        auto oldest = g_jit_cache.end();
+        for (auto it = g_jit_cache.begin(); it != g_jit_cache.end(); ++it) {
+            if (it->second.refs > 0) continue;
+            ++idle;
+            if (oldest == g_jit_cache.end() || it->second.last_use < oldest->second.last_use) oldest = it;
+        }
+        if (idle <= kJitIdleLimit || oldest == g_jit_cache.end()) return;
+        unload_on(oldest->first.device, oldest->second.module);
+        g_jit_by_function.erase(oldest->second.function);
+        g_jit_cache.erase(oldest);
+    }
+}
 
 }  // namespace
 
@@ -370,13 +431,18 @@ int mcd_jit_kernel(int device, const char* source, const char* kernel_name, cons
     if (compile_ms != nullptr) *compile_ms = 0.0;
     const DriverApi* drv = driver_api();
     if (drv == nullptr) return fail("the CUDA driver API is unavailable (no driver on this machine?)");
-    std::lock_guard<std::mutex> lock(g_jit_mutex);
-    auto key = std::make_tuple(device, std::string(options != nullptr ? options : ""), std::string(source),
-                               std::string(kernel_name));
-    const auto hit = g_jit_cache.find(key);
-    if (hit != g_jit_cache.end()) {
-        *function = hit->second.function;
-        return 0;
+    const std::size_t length = std::strlen(source);
+    const JitKey key{device, std::string(options != nullptr ? options : ""), std::string(kernel_name), fnv1a64(source, length),
+                     length};
+    {
+        std::lock_guard<std::mutex> lock(g_jit_mutex);
+        const auto hit = g_jit_cache.find(key);
+        if (hit != g_jit_cache.end()) {
+            ++hit->second.refs;
+            hit->second.last_use = ++g_jit_clock;
+            *function = hit->second.function;
+            return 0;
+        }
     }
     int current = -1;
     if (int rc = check_rt(cudaGetDevice(&current), "cudaGetDevice")) return rc;
@@ -392,11 +458,51 @@ int mcd_jit_kernel(int device, const char* source, const char* kernel_name, cons
     if (rc == 0) rc = check_drv(drv->ModuleLoadData(&entry.module, cubin.data()), "cuModuleLoadData");
     if (rc == 0) rc = check_drv(drv->ModuleGetFunction(&entry.function, entry.module, kernel_name), "cuModuleGetFunction");
     const auto t1 = std::chrono::steady_clock::now();
+    if (rc != 0 && entry.module != nullptr) drv->ModuleUnload(entry.module);
     if (current != device) cudaSetDevice(current);
     if (rc != 0) return rc;
     if (compile_ms != nullptr) *compile_ms = std::chrono::duration<double, std::milli>(t1 - t0).count();
-    g_jit_cache.emplace(std::move(key), entry);
+
+    std::lock_guard<std::mutex> lock(g_jit_mutex);
+    const auto raced = g_jit_cache.find(key);
+    if (raced != g_jit_cache.end()) {
+        // Another thread compiled the same kernel meanwhile: keep its module, drop ours.
+        unload_on(device, entry.module);
+        ++raced->second.refs;
+        raced->second.last_use = ++g_jit_clock;
+        *function = raced->second.function;
+        return 0;
+    }
+    entry.refs = 1;
+    entry.last_use = ++g_jit_clock;
+    g_jit_by_function.emplace(entry.function, key);
+    g_jit_cache.emplace(key, entry);
     *function = entry.function;
+    evict_idle_locked();
+    return 0;
+}
+
+int mcd_jit_release(void* function) {
+    if (function == nullptr) return 0;
+    std::lock_guard<std::mutex> lock(g_jit_mutex);
+    const auto key = g_jit_by_function.find(function);
+    if (key == g_jit_by_function.end()) return fail("mcd_jit_release: not a kernel of mcd_jit_kernel (or released too often)");
+    const auto entry = g_jit_cache.find(key->second);
+    if (entry == g_jit_cache.end() || entry->second.refs <= 0) return fail("mcd_jit_release: released more often than obtained");
+    --entry->second.refs;
+    evict_idle_locked();
+    return 0;
+}
+
+int mcd_jit_cache_stats(long long* modules, long long* idle) {
+    std::lock_guard<std::mutex> lock(g_jit_mutex);
+    long long n = 0, unused = 0;
+    for (const auto& kv : g_jit_cache) {
+        ++n;
+        if (kv.second.refs == 0) ++unused;
+    }
+    if (modules != nullptr) *modules = n;
+    if (idle != nullptr) *idle = unused;
     return 0;
 }
 

@@ -7,6 +7,7 @@
 #include "minicompiler_b200_device.h"
 
 #include "device/driver_api.hpp"
+#include "device/per_device.hpp"
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -15,7 +16,10 @@
 #include <atomic>
 #include <cstdint>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <string>
+#include <tuple>
 
 #include "kernels/epilogue.cuh"
 #include "kernels/gemm_f32_simt.cuh"
@@ -118,6 +122,15 @@ int sm_count_of_current_device() {
     if (sms <= 0) sms = 148;
     if (dev >= 0 && dev < 64) cached[dev] = sms;
     return sms;
+}
+
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return dev;
 }
 
 int launched(const char* what) {
@@ -239,18 +252,51 @@ unsigned instruction_descriptor(int arith, bool b_is_k_major) {
     return d;
 }
 
+// cuTensorMapEncodeTiled is a pure function of its arguments, and an executable launches the same matmuls on the same
+// arena addresses over and over: the encoded maps are kept, so a launch outside a replayed graph pays two look-ups
+// instead of two driver calls (several microseconds, which shows on problems of 15 us).
+struct MapKey {
+    const void* base;
+    unsigned long long inner, outer, pitch;
+    unsigned box_inner, box_outer;
+    int type, elem_bytes;
+    bool operator<(const MapKey& o) const {
+        return std::tie(base, inner, outer, pitch, box_inner, box_outer, type, elem_bytes) <
+               std::tie(o.base, o.inner, o.outer, o.pitch, o.box_inner, o.box_outer, o.type, o.elem_bytes);
+    }
+};
+std::mutex g_map_mutex;
+std::map<MapKey, CUtensorMap> g_map_cache;
+std::atomic<unsigned long long> g_map_encodes{0};
+
 int encode_map(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, unsigned long long inner,
                unsigned long long outer, unsigned long long pitch_elems, unsigned box_inner, unsigned box_outer) {
+    const MapKey key{base, inner, outer, pitch_elems, box_inner, box_outer, static_cast<int>(type), elem_bytes};
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        const auto hit = g_map_cache.find(key);
+        if (hit != g_map_cache.end()) {
+            *map = hit->second;
+            return 0;
+        }
+    }
     const DriverApi* drv = driver_api();
     if (drv == nullptr) return fail("the CUDA driver API is unavailable");
     const cuuint64_t dims[2] = {inner, outer};
     const cuuint64_t strides[1] = {pitch_elems * static_cast<unsigned long long>(elem_bytes)};
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t elem_strides[2] = {1, 1};
-    return check_drv(drv->TensorMapEncodeTiled(map, type, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
-                     "cuTensorMapEncodeTiled");
+    if (int rc = check_drv(drv->TensorMapEncodeTiled(map, type, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+                           "cuTensorMapEncodeTiled")) {
+        return rc;
+    }
+    g_map_encodes.fetch_add(1, std::memory_order_relaxed);
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    if (g_map_cache.size() >= 4096) g_map_cache.clear();  // a bound, not a policy: maps are cheap to make again
+    g_map_cache.emplace(key, *map);
+    return 0;
 }
 
 // K blocks and effective K splits of a tensor-core launch.
@@ -375,16 +421,18 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
         using PairKernel = void (*)(const McTensorMap, const McTensorMap, const McTcParams, const McEpilogueArgs);
         PairKernel kernel = p.wide ? (tf32 ? mc_gemm_tc2w_tf32_bk : (b_k_major ? mc_gemm_tc2w_h16_bk : mc_gemm_tc2w_h16_bmn))
                                    : (tf32 ? mc_gemm_tc2_tf32_bk : (b_k_major ? mc_gemm_tc2_h16_bk : mc_gemm_tc2_h16_bmn));
-        static std::atomic<int> pair_configured{0};
-        if (pair_configured.load() == 0) {
+        // The opt-in to more than 48 KB of dynamic shared memory is kept per device.
+        static PerDeviceOnce pair_configured;
+        const int device = current_device();
+        if (pair_configured.first_use(device)) {
             for (PairKernel kfn : {mc_gemm_tc2_tf32_bk, mc_gemm_tc2_h16_bk, mc_gemm_tc2_h16_bmn, mc_gemm_tc2w_tf32_bk,
                                    mc_gemm_tc2w_h16_bk, mc_gemm_tc2w_h16_bmn}) {
                 if (int rc = check_rt(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_TC2_SMEM_BYTES),
                                       "cudaFuncSetAttribute(max dynamic shared memory)")) {
+                    pair_configured.forget(device);
                     return rc;
                 }
             }
-            pair_configured.store(1);
         }
         kernel<<<pair_grid, MC_TC_THREADS, MC_TC2_SMEM_BYTES, s>>>(map_a, map_b, p, epi);
         return launched("mc_gemm_tc2");
@@ -400,15 +448,16 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     using Kernel = void (*)(const McTensorMap, const McTensorMap, const McTcParams, const McEpilogueArgs);
     Kernel kernel = tf32 ? (b_k_major ? mc_gemm_tc_tf32_bk : mc_gemm_tc_tf32_bmn)
                          : (b_k_major ? mc_gemm_tc_h16_bk : mc_gemm_tc_h16_bmn);
-    static std::atomic<int> configured{0};
-    if (configured.load() != 0xF) {
+    static PerDeviceOnce configured;
+    const int device = current_device();
+    if (configured.first_use(device)) {
         for (Kernel kfn : {mc_gemm_tc_tf32_bk, mc_gemm_tc_tf32_bmn, mc_gemm_tc_h16_bk, mc_gemm_tc_h16_bmn}) {
             if (int rc = check_rt(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_TC_SMEM_BYTES),
                                   "cudaFuncSetAttribute(max dynamic shared memory)")) {
+                configured.forget(device);
                 return rc;
             }
         }
-        configured.store(0xF);
     }
     kernel<<<grid, MC_TC_THREADS, MC_TC_SMEM_BYTES, s>>>(map_a, map_b, p, epi);
     if (int rc = launched("mc_gemm_tc")) return rc;
@@ -482,6 +531,12 @@ extern "C" size_t mcd_gemm_dynamic_smem(int arith) {
     static_assert(MC_TC2_SMEM_BYTES >= MC_TC_SMEM_BYTES, "the pair kernels set the limit of both tensor-core families");
     static_assert(MC_TC2_SMEM_BYTES + 64 <= 227 * 1024, "dynamic plus static shared memory of the pair kernel");
     return (arith == MCD_GEMM_TF32 || arith == MCD_GEMM_BF16 || arith == MCD_GEMM_F16) ? MC_TC2_SMEM_BYTES : 0;
+}
+
+extern "C" int mcd_per_device_once_probe(const int* devices, int count, int* first) {
+    PerDeviceOnce flag;
+    for (int i = 0; i < count; ++i) first[i] = flag.first_use(devices[i]) ? 1 : 0;
+    return 0;
 }
 
 extern "C" int mcd_tensor_core_supported(int device, int arith) {

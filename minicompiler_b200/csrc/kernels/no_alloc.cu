@@ -7,9 +7,12 @@
 // Such callers cannot use the split-K path of mcd_gemm, because that one expects the
 // caller to bring a workspace of splits*m*n floats for the partial sums.
 //
-// Here the partial sums live in a fixed array that is part of the library image: every
-// GPU that loads the library holds MCD_NO_ALLOC_SCRATCH_BYTES of it until the process
-// exits. The kernels are the very same source as the regular path (the .cuh files are
+// Here the partial sums live in a fixed array that is part of the library image. CUDA
+// loads the module that owns it lazily, so a GPU starts to hold its
+// MCD_NO_ALLOC_SCRATCH_BYTES on the FIRST call made on it (that call may allocate and
+// synchronise inside the driver, so it belongs at start-up, before the caller's pool
+// takes the rest of HBM and before any stream capture; a tiny splits = 1 problem will
+// do) and keeps them until the process exits. The kernels are the very same source as the regular path (the .cuh files are
 // included a second time under other entry-point names), so results are bit-identical
 // to mcd_gemm with the same split count.
 

@@ -387,10 +387,8 @@ def test_config_graphs_small(mc, oracle):
                     ok, msg = all_close(got, want, tol, tol * scale)
                     assert ok, f"{name} {matmul} fuse={fuse}: {msg}"
                 else:
-                    err = norm_scaled_error(got, want)
-                    # deep stacks accumulate the per-layer rounding; the bar is per matmul layer
-                    layers = 8 if name.startswith("c5") else 2 if name.startswith("c3") else 1
-                    assert err <= tol * layers, f"{name} {matmul} fuse={fuse}: norm-scaled error {err:.3e}"
+                    err = norm_scaled_error(got, want)  # end to end, at the bar itself, whatever the depth
+                    assert err <= tol, f"{name} {matmul} fuse={fuse}: norm-scaled error {err:.3e}"
 
 
 def test_c2_gelu_full_size_properties(mc, oracle):

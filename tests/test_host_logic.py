@@ -555,3 +555,46 @@ def test_sharding_rules_for_row_reductions(mc, tmp_path):
     flat.write_text("dim B = 64\ninput x : f32[B]\ns = row_sum x\noutput s\n")
     with pytest.raises(mc.McError, match="row_sum 's' reduces over dim 'B'"):
         mc.shard_dims(str(flat), {}, "B", 0, 2)
+
+
+# ------------------------------------------------ host-side guards of the device path
+
+
+def test_in_place_run_needs_16_byte_aligned_buffers_for_vectorised_kernels(mc):
+    """mc_run lets streaming kernels work on pinned caller memory in place. A vectorised kernel moves 128 bits per
+    access, so a buffer that starts off a 16-byte boundary (a view into a pinned allocation) must take the staged
+    path; the predicate behind that decision is checked here without touching a GPU."""
+    lib = mc.lib()
+
+    def ok(addresses, vectorised):
+        arr = (ctypes.c_void_p * len(addresses))(*addresses)
+        return lib.mcb_in_place_pointers_ok(arr, len(addresses), int(vectorised))
+
+    assert ok([0x7F0000000000, 0x7F0000001000], True) == 1
+    assert ok([0x7F0000000000, 0x7F0000001004], True) == 0   # t[1:] of a float tensor
+    assert ok([0x7F0000000008], True) == 0
+    assert ok([0x7F0000000004, 0x7F0000001004], False) == 1  # scalar kernels have no such requirement
+    assert ok([], True) == 1
+
+
+def test_per_device_kernel_set_up_runs_once_on_every_device(mc):
+    """The opt-in to large dynamic shared memory is a per-device attribute of a kernel: the bookkeeping must ask for
+    it on the first launch on each GPU a process drives, not once per process."""
+    lib = mc.lib()
+    devices = [0, 0, 1, 0, 1, 2, 63, 63, 64, 64, -1]
+    first = (ctypes.c_int * len(devices))()
+    assert lib.mcd_per_device_once_probe((ctypes.c_int * len(devices))(*devices), len(devices), first) == 0
+    # ordinals outside 0..63 are not remembered, so their set-up repeats (harmless) instead of being skipped
+    assert list(first) == [1, 0, 1, 0, 0, 1, 1, 0, 1, 1, 1]
+
+
+def test_no_tensor_can_outgrow_the_32_bit_indices_of_the_generated_kernels(mc):
+    """The generated kernels count and index elements in unsigned 32 bits and add one trip of their grid-stride
+    loop before testing the bound. The format caps a tensor at 2^31 - 1 elements (src/parser.cpp shape check), so
+    index + trip stays below 2^32: larger tensors never reach lowering."""
+    for shape in ("[65536, 65536]", "[32768, 65536]", "[1048576, 4096]"):
+        with pytest.raises(mc.McError, match=r"at most 2\^31 - 1 elements"):
+            mc.HostGraph(text=f"input x : f32{shape}\ny = exp x\noutput y", passes="none")
+    fine = "input x : f32[32768, 65535]\ny = exp x\ns = row_sum y\noutput s"
+    plan = mc.HostGraph(text=fine, passes="none").launch_plan()
+    assert plan.strip()
