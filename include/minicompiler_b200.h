@@ -87,6 +87,11 @@ MC_EXPORT int mc_refresh_constants(void* handle);
  * mc_download then fail with a message and clear it. Exposed so that this error path can be exercised from
  * the host (write a non-zero value with mcd_copy_h2d) without making any kernel wait. */
 MC_EXPORT int mc_status_word_ptr(void* handle, void** device_ptr);
+/* Row slices mc_run cuts a call on pinned host buffers into, so that the copy-in of one slice, the kernels of
+ * the previous and the copy-out of the one before overlap (option host_io_row_slices, default 16); 0 when the
+ * graph's rows are not independent, it moves too little, or it is a single streaming kernel (which has a
+ * pipeline of its own). Results are bit-identical to the unsliced run. */
+MC_EXPORT int mc_row_slices(void* handle);
 /* Device address of input / output k (float32, dense, graph layout). */
 MC_EXPORT int mc_input_device_ptr(void* handle, int k, void** device_ptr, size_t* elements);
 MC_EXPORT int mc_output_device_ptr(void* handle, int k, void** device_ptr, size_t* elements);
@@ -119,6 +124,10 @@ MC_EXPORT int mcb_graph_plan_json(const void* graph, int pool_outputs, char* out
 MC_EXPORT int mcb_graph_fusion_groups(const void* graph, char* out, int size);   /* find_fusion_groups, names */
 MC_EXPORT int mcb_graph_emit_cuda(const void* graph, const char* options, char* out, int size); /* --emit-cuda */
 MC_EXPORT int mcb_graph_launch_plan(const void* graph, const char* options, int sm_count, char* out, int size);
+/* Row slicing of mc_run on pinned memory (no counterpart: the reference copies in, runs, copies out): "none", or
+ * "rows=<leading extent> cut=<names of the values cut by rows>"; with slice_rows > 0 followed by the printed graph
+ * at that row count. -1 with a message when the slice-sized graph cannot be built. */
+MC_EXPORT int mcb_graph_row_slicing(const void* graph, long long slice_rows, char* out, int size);
 MC_EXPORT int mcb_graph_num_nodes(const void* graph);
 /* Copies the values of constant node `name` (after the passes); returns the element count or -1. */
 MC_EXPORT long long mcb_graph_constant(const void* graph, const char* name, float* out, long long capacity);

@@ -59,6 +59,7 @@ def lib() -> C.CDLL:
         "mc_constants_region": (i32, [vp, C.POINTER(vp), C.POINTER(C.c_size_t)]),
         "mc_refresh_constants": (i32, [vp]),
         "mc_status_word_ptr": (i32, [vp, C.POINTER(vp)]),
+        "mc_row_slices": (i32, [vp]),
         "mcb_in_place_pointers_ok": (i32, [C.POINTER(vp), i32, i32]),
         "mcd_copy_h2d": (i32, [vp, vp, C.c_size_t, vp]),
         "mcd_copy_d2h": (i32, [vp, vp, C.c_size_t, vp]),
@@ -82,6 +83,7 @@ def lib() -> C.CDLL:
         "mcb_graph_launch_plan": (i32, [vp, cp, i32, cp, i32]),
         "mcb_graph_plan_sources": (i32, [vp, cp, i32, cp, i32]),
         "mcb_graph_num_nodes": (i32, [vp]),
+        "mcb_graph_row_slicing": (i32, [vp, i64, cp, i32]),
         "mcb_graph_constant": (i64, [vp, cp, C.POINTER(C.c_float), i64]),
         "mcb_graph_check_kernels": (i32, [vp, cp, i32]),
         "mcb_uniform_values": (None, [C.POINTER(C.c_float), i64, C.c_ulonglong, C.c_float, C.c_float]),
@@ -277,6 +279,11 @@ class CompiledGraph:
         if lib().mc_refresh_constants(self._h) != 0:
             raise McError(_last_error())
 
+    @property
+    def row_slices(self) -> int:
+        """Slices mc_run cuts a call on pinned host buffers into (0: not sliced)."""
+        return lib().mc_row_slices(self._h)
+
     def status_word_ptr(self) -> int:
         """Device address of the status word (0 when no kernel of this graph can wait)."""
         ptr = C.c_void_p()
@@ -349,6 +356,11 @@ class HostGraph:
     def plan_sources(self, options=None, sm_count: int = 148) -> str:
         """The CUDA text the launch plan generates, step by step (no GPU needed)."""
         return _read_string(lib().mcb_graph_plan_sources, self._g, _enc(_opts_str(options)), sm_count)
+
+    def row_slicing(self, slice_rows: int = 0) -> str:
+        """Which values mc_run may cut by rows ("none" or "rows=N cut=a,b,..."), optionally with the graph at
+        `slice_rows` rows printed after it."""
+        return _read_string(lib().mcb_graph_row_slicing, self._g, slice_rows)
 
     def constant(self, name: str) -> np.ndarray:
         n = lib().mcb_graph_constant(self._g, name.encode(), None, 0)

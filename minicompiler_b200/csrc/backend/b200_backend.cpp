@@ -1,5 +1,7 @@
 #include "backend/b200_backend.hpp"
 
+#include "backend/row_slicing.hpp"
+
 #include "minicompiler_b200_device.h"
 
 #include <algorithm>
@@ -53,7 +55,12 @@ struct Launch {
     long long rows = 0, cols = 0, src_pitch = 0, dst_pitch = 0;
     int transpose = 0;
     int half_kind = 0;  // 0: FP32 transpose
+    // Row slicing: bytes by which each pointer moves per row of the cut dimension (0: the tensor is not cut).
+    // Elementwise kinds: one entry per `pointers` slot. Matmul: a, c, c16, then the epilogue inputs. Recast: src, dst.
+    std::vector<std::size_t> row_bytes;
 };
+
+using LaunchList = std::vector<std::unique_ptr<Launch>>;
 
 class B200Executable final : public CudaExecutable {
 public:
@@ -110,6 +117,8 @@ public:
                          std::to_string(graph_.outputs().size()) + " output buffers"};
         }
         bool done = false;
+        MC_TRY(run_in_row_slices(inputs, outputs, &done));
+        if (done) return Status();
         MC_TRY(run_on_host_memory(inputs, outputs, &done));
         if (done) return Status();
         MC_TRY(upload_inputs(inputs));
@@ -117,7 +126,7 @@ public:
         return download_outputs(outputs);
     }
 
-    std::size_t intermediate_bytes() const override { return lowered_.pool.bytes_with_reuse(); }
+    std::size_t intermediate_bytes() const override { return lowered_.pool.bytes_with_reuse() + unpooled_output_bytes_; }
 
     Status upload_inputs(const std::vector<const float*>& host_inputs) override {
         if (host_inputs.size() != graph_.inputs().size()) return Error{"wrong number of inputs"};
@@ -189,6 +198,7 @@ public:
 
     void* status_word_address() const override { return uses_status_ ? status_word() : nullptr; }
 
+    std::size_t row_slices() const override { return slice_rows_ > 0 ? static_cast<std::size_t>(slicing_.rows / slice_rows_) : 0; }
     std::size_t arena_bytes() const override { return arena_bytes_; }
     std::string plan_description() const override { return describe(graph_, lowered_); }
 
@@ -205,6 +215,104 @@ public:
 
 private:
     B200Executable(const Graph& graph, const CudaOptions& options) : graph_(graph), options_(options) {}
+
+    // run() in row slices, three stages deep, for row-independent graphs on pinned caller memory: while slice i is
+    // computed, slice i+1 comes in on one copy engine and slice i-1 goes out on the other. Every slice runs the
+    // launches of the slice-sized plan with its pointers moved down by the slice's first row; slices follow one
+    // another on the compute stream, so intermediates of different slices never coexist, and outputs live outside
+    // the buffer pool, so a later slice cannot touch rows that are still being copied out. Sets *done when it ran.
+    Status run_in_row_slices(const std::vector<const float*>& inputs, const std::vector<float*>& outputs, bool* done) {
+        *done = false;
+        if (slice_rows_ == 0) return Status();
+        for (const float* p : inputs) {
+            void* alias = nullptr;
+            if (mcd_host_device_pointer(p, &alias) != 0) return Status();  // pageable memory: copies would not overlap
+        }
+        for (float* p : outputs) {
+            void* alias = nullptr;
+            if (mcd_host_device_pointer(p, &alias) != 0) return Status();
+        }
+        MCD_TRY(mcd_set_device(options_.device));
+        const std::size_t slices = slice_in_.size();
+        for (std::size_t c = 0; c < slices; ++c) {
+            const std::size_t first_row = c * static_cast<std::size_t>(slice_rows_);
+            for (std::size_t k = 0; k < inputs.size(); ++k) {
+                const NodeId id = graph_.inputs()[k];
+                const std::size_t per_row = row_bytes(graph_, id, kRepF32);
+                if (per_row > 0) {
+                    MCD_TRY(mcd_copy_h2d(address(id, kRepF32) + first_row * per_row,
+                                         reinterpret_cast<const char*>(inputs[k]) + first_row * per_row,
+                                         static_cast<std::size_t>(slice_rows_) * per_row, copy_in_));
+                } else if (c == 0) {
+                    MCD_TRY(mcd_copy_h2d(address(id, kRepF32), inputs[k], graph_.node(id).type.size_bytes(), copy_in_));
+                }
+            }
+            MCD_TRY(mcd_event_record(slice_in_[c], copy_in_));
+            MCD_TRY(mcd_stream_wait_event(stream_, slice_in_[c]));
+            if (c == 0) {
+                // 16-bit / transposed forms of inputs that are not cut are made once, from the whole tensor.
+                for (const Launch& l : upload_recasts_) {
+                    if (l.row_bytes[0] == 0) MC_TRY(issue(l, stream_));
+                }
+            }
+            for (const Launch& l : slice_upload_recasts_) {
+                if (l.row_bytes[0] != 0) MC_TRY(issue_at_row(l, first_row, stream_));
+            }
+            for (const std::unique_ptr<Launch>& l : slice_launches_) MC_TRY(issue_at_row(*l, first_row, stream_));
+            MCD_TRY(mcd_event_record(slice_done_[c], stream_));
+            MCD_TRY(mcd_stream_wait_event(copy_out_, slice_done_[c]));
+            for (std::size_t k = 0; k < outputs.size(); ++k) {
+                const NodeId id = graph_.outputs()[k];
+                const std::size_t per_row = row_bytes(graph_, id, kRepF32);
+                MCD_TRY(mcd_copy_d2h(reinterpret_cast<char*>(outputs[k]) + first_row * per_row,
+                                     address(id, kRepF32) + first_row * per_row, static_cast<std::size_t>(slice_rows_) * per_row,
+                                     copy_out_));
+            }
+        }
+        MCD_TRY(mcd_stream_synchronize(copy_out_));
+        MCD_TRY(mcd_stream_synchronize(stream_));
+        MC_TRY(check_status_word());
+        *done = true;
+        return Status();
+    }
+
+    // One launch of the slice-sized plan, with every pointer into a cut tensor moved down to `first_row`.
+    Status issue_at_row(const Launch& l, std::size_t first_row, void* stream) const {
+        auto moved = [&](const void* p, std::size_t per_row) {
+            return p == nullptr ? nullptr : const_cast<char*>(static_cast<const char*>(p)) + first_row * per_row;
+        };
+        switch (l.kind) {
+            case Launch::Kind::Elementwise: {
+                std::vector<void*> pointers(l.pointers.size());
+                for (std::size_t i = 0; i < pointers.size(); ++i) pointers[i] = moved(l.pointers[i], l.row_bytes[i]);
+                std::vector<void*> params;
+                for (void*& p : pointers) params.push_back(&p);
+                unsigned count = l.count;
+                params.push_back(&count);
+                MCD_TRY(mcd_launch(l.function, l.grid, 1, 1, l.block, 0, stream, params.data()));
+                return Status();
+            }
+            case Launch::Kind::Matmul: {
+                mcd_gemm_args g = l.gemm;
+                g.a = moved(g.a, l.row_bytes[0]);
+                g.c = static_cast<float*>(static_cast<void*>(moved(g.c, l.row_bytes[1])));
+                g.c16 = moved(g.c16, l.row_bytes[2]);
+                for (int i = 0; i < g.num_epilogue_inputs; ++i) {
+                    g.epilogue_inputs[i] = static_cast<const float*>(static_cast<const void*>(
+                        moved(g.epilogue_inputs[i], l.row_bytes[3 + static_cast<std::size_t>(i)])));
+                }
+                MCD_TRY(mcd_gemm(&g, stream));
+                return Status();
+            }
+            case Launch::Kind::Recast: {
+                Launch at = l;
+                at.src = static_cast<const float*>(static_cast<const void*>(moved(l.src, l.row_bytes[0])));
+                at.dst = moved(l.dst, l.row_bytes[1]);
+                return issue(at, stream);
+            }
+        }
+        return Status();
+    }
 
     // run() without staging copies, for graphs that only stream: when every step is a generated elementwise
     // kernel, every graph input is read by exactly one of them and every output is written by one and read by
@@ -415,8 +523,8 @@ private:
         return Status();
     }
 
-    Launch make_recast(const Recast& rc) const {
-        const TensorType& type = graph_.node(rc.node).type;
+    Launch make_recast(const Graph& graph, const Recast& rc) const {
+        const TensorType& type = graph.node(rc.node).type;
         Launch l;
         l.kind = Launch::Kind::Recast;
         l.src = reinterpret_cast<const float*>(address(rc.node, kRepF32));
@@ -441,7 +549,20 @@ private:
                 l.dst_pitch = (l.rows + 3) / 4 * 4;
                 break;
         }
+        l.row_bytes = {row_bytes(graph, rc.node, kRepF32), row_bytes(graph, rc.node, rc.to)};
         return l;
+    }
+
+    // Bytes between consecutive rows of the cut dimension in form `rep` of `node`; 0 when the value is not cut.
+    std::size_t row_bytes(const Graph& graph, NodeId node, Rep rep) const {
+        if (!slicing_.ok || !slicing_.carries[static_cast<std::size_t>(node)]) return 0;
+        const TensorType& type = graph.node(node).type;
+        const std::size_t per_row = type.num_elements() / static_cast<std::size_t>(type.shape[0]);
+        switch (rep) {
+            case kRepF32: return per_row * sizeof(float);
+            case kRepHalf: return (type.rank() == 2 ? static_cast<std::size_t>(half_pitch(type.shape[1])) : per_row) * 2;
+            default: return 0;  // transposed forms are never cut (their rows are the other dimension)
+        }
     }
 
     Status init() {
@@ -456,10 +577,19 @@ private:
         MCD_TRY(mcd_set_device(options_.device));
         MCD_TRY(mcd_stream_create(&stream_));
 
-        MC_ASSIGN(lowered, lower_graph(graph_, options_, device_.sm_count));
+        // Row slicing for run() on pinned memory is decided first: it changes where outputs live.
+        MC_TRY(plan_row_slices());
+        MC_ASSIGN(lowered, lower_graph(graph_, options_, device_.sm_count, /*pool_outputs=*/slice_rows_ == 0));
         lowered_ = std::move(lowered);
+        if (slice_rows_ > 0) {
+            MC_TRY(lower_row_slices());
+            if (slice_rows_ == 0) {  // the slice-sized graph lowers differently: outputs go back into the pool
+                MC_ASSIGN(again, lower_graph(graph_, options_, device_.sm_count, true));
+                lowered_ = std::move(again);
+            }
+        }
 
-        // ---- arena layout: constants | inputs | pooled buffers | split-K workspace | status word
+        // ---- arena layout: constants | inputs | outputs kept out of the pool | pooled buffers | split-K workspace | status word
         const std::size_t count = graph_.num_nodes();
         offset_.assign(count * kNumReps, kNoOffset);
         std::size_t cursor = 0;
@@ -477,6 +607,14 @@ private:
         place_leaves(OpKind::Constant);
         constants_bytes_ = cursor;
         place_leaves(OpKind::Input);
+        unpooled_output_bytes_ = 0;
+        for (std::size_t v = 0; v < lowered_.pool_values.size(); ++v) {
+            const PoolValue& value = lowered_.pool_values[v];
+            if (value.pooled || !value.live_out || !is_compute(graph_.node(static_cast<NodeId>(v / kNumReps)).op)) continue;
+            offset_[v] = cursor;
+            cursor += align_up(value.bytes);
+            unpooled_output_bytes_ += value.bytes;
+        }
         std::vector<std::size_t> buffer_offset(lowered_.pool.buffer_bytes.size());
         for (std::size_t b = 0; b < buffer_offset.size(); ++b) {
             buffer_offset[b] = cursor;
@@ -486,15 +624,15 @@ private:
             const std::int32_t b = lowered_.pool.buffer_of[v];
             if (b != PoolPlan::kNotPooled) offset_[v] = buffer_offset[static_cast<std::size_t>(b)];
         }
+        const std::size_t workspace_bytes = std::max(lowered_.workspace_bytes, slice_rows_ > 0 ? slice_lowered_.workspace_bytes : 0);
         const std::size_t workspace_offset = cursor;
-        cursor += align_up(lowered_.workspace_bytes);
+        cursor += align_up(workspace_bytes);
         status_offset_ = cursor;
         cursor += kAlign;
         arena_bytes_ = cursor;
         MCD_TRY(mcd_malloc(&arena_, arena_bytes_));
         MCD_TRY(mcd_memset(status_word(), 0, kAlign, stream_));
-        float* workspace = lowered_.workspace_bytes > 0 ? reinterpret_cast<float*>(static_cast<char*>(arena_) + workspace_offset)
-                                                        : nullptr;
+        float* workspace = workspace_bytes > 0 ? reinterpret_cast<float*>(static_cast<char*>(arena_) + workspace_offset) : nullptr;
 
         // ---- constants: uploaded once, derived forms made once
         for (std::size_t i = 0; i < count; ++i) {
@@ -502,30 +640,31 @@ private:
             if (n.op != OpKind::Constant) continue;
             MCD_TRY(mcd_copy_h2d(address(static_cast<NodeId>(i), kRepF32), n.constant->data(), n.type.size_bytes(), stream_));
         }
-        for (const Recast& rc : lowered_.at_compile) constant_recasts_.push_back(make_recast(rc));
-        for (const Recast& rc : lowered_.after_upload) upload_recasts_.push_back(make_recast(rc));
+        for (const Recast& rc : lowered_.at_compile) constant_recasts_.push_back(make_recast(graph_, rc));
+        for (const Recast& rc : lowered_.after_upload) upload_recasts_.push_back(make_recast(graph_, rc));
         for (const Launch& l : constant_recasts_) MC_TRY(issue(l, stream_));
         MCD_TRY(mcd_stream_synchronize(stream_));
 
         // ---- launches
-        for (std::size_t i = 0; i < lowered_.steps.size(); ++i) {
-            const Step& step = lowered_.steps[i];
-            if (step.kind == Step::Kind::Elementwise) {
-                MC_TRY(add_elementwise(step));
-            } else if (step.kind == Step::Kind::RowFused) {
-                MC_TRY(add_row_fused(step));
-            } else if (step.kind == Step::Kind::Reduce) {
-                MC_TRY(add_reduce(step));
-            } else {
-                MC_TRY(add_matmul(step, workspace));
+        MC_TRY(build_launches(graph_, lowered_, workspace, launches_));
+        if (slice_rows_ > 0) {
+            MC_TRY(build_launches(slice_graph_, slice_lowered_, workspace, slice_launches_));
+            for (const Recast& rc : slice_lowered_.after_upload) slice_upload_recasts_.push_back(make_recast(slice_graph_, rc));
+            MCD_TRY(mcd_stream_create(&copy_in_));
+            MCD_TRY(mcd_stream_create(&copy_out_));
+            const std::size_t slices = static_cast<std::size_t>(slicing_.rows / slice_rows_);
+            slice_in_.assign(slices, nullptr);
+            slice_done_.assign(slices, nullptr);
+            for (std::size_t c = 0; c < slices; ++c) {
+                MCD_TRY(mcd_event_create(&slice_in_[c]));
+                MCD_TRY(mcd_event_create(&slice_done_[c]));
             }
-            for (const Recast& rc : lowered_.after_step[i]) launches_.push_back(std::make_unique<Launch>(make_recast(rc)));
         }
         // Every buffer address is fixed for the life of the executable, so the launch list can be recorded
         // once and replayed: one graph launch per enqueue instead of one driver call (and, for tensor-core
         // matmuls, two tensor-map encodings) per kernel. The list runs once for real first, so that one-time
         // kernel set-up does not happen inside the recording.
-        streams_only_ = graph_only_streams();
+        streams_only_ = slice_rows_ == 0 && graph_only_streams();
         pipeline_elements_ = pipeline_elements();
         if (pipeline_elements_ > 0) {
             MCD_TRY(mcd_stream_create(&copy_in_));
@@ -557,10 +696,97 @@ private:
         return Status();
     }
 
-    Status add_elementwise(const Step& step) {
-        const Node& node = graph_.node(step.result);
+    Status build_launches(const Graph& graph, const LoweredGraph& lowered, float* workspace, LaunchList& list) {
+        for (std::size_t i = 0; i < lowered.steps.size(); ++i) {
+            const Step& step = lowered.steps[i];
+            if (step.kind == Step::Kind::Elementwise) {
+                MC_TRY(add_elementwise(graph, step, list));
+            } else if (step.kind == Step::Kind::RowFused) {
+                MC_TRY(add_row_fused(graph, step, list));
+            } else if (step.kind == Step::Kind::Reduce) {
+                MC_TRY(add_reduce(graph, step, list));
+            } else {
+                MC_TRY(add_matmul(graph, step, workspace, list));
+            }
+            for (const Recast& rc : lowered.after_step[i]) list.push_back(std::make_unique<Launch>(make_recast(graph, rc)));
+        }
+        return Status();
+    }
+
+    // Decides whether run() on pinned memory works in row slices, and how many rows a slice has (slice_rows_;
+    // 0 = no). Worth it for graphs that are not one streaming elementwise launch (those have a path of their
+    // own), whose rows are independent, and that move enough bytes over the bus for the overlap to pay.
+    Status plan_row_slices() {
+        slice_rows_ = 0;
+        if (options_.host_io != 1 || options_.host_io_row_slices < 2) return Status();
+        bool has_heavy_node = false;
+        for (const Node& n : graph_.nodes()) has_heavy_node = has_heavy_node || n.op == OpKind::MatMul || is_row_reduce(n.op);
+        if (!has_heavy_node) return Status();
+        slicing_ = analyze_row_slicing(graph_);
+        if (!slicing_.ok) return Status();
+        std::size_t moved = 0;
+        for (NodeId in : graph_.inputs()) moved += graph_.node(in).type.size_bytes();
+        for (NodeId out : graph_.outputs()) moved += graph_.node(out).type.size_bytes();
+        if (moved < kMinSlicedBytes) {
+            slicing_ = RowSlicing{};
+            return Status();
+        }
+        // The largest slice count up to the requested one that divides the rows into multiples of 128 (whole tiles).
+        for (std::int64_t slices = options_.host_io_row_slices; slices >= 2; --slices) {
+            if (slicing_.rows % slices == 0 && (slicing_.rows / slices) % 128 == 0) {
+                slice_rows_ = slicing_.rows / slices;
+                break;
+            }
+        }
+        if (slice_rows_ == 0) slicing_ = RowSlicing{};
+        return Status();
+    }
+
+    // Lowers the graph at the slice's row count and checks that it is the same plan as the full one: same steps in
+    // the same order defining the same forms, so that the slice's launches can use the full plan's addresses.
+    // K splits are taken from the full plan, so a slice adds every output's products in the same order as the
+    // unsliced run (results are bit-identical). Anything else turns slicing off (slice_rows_ = 0).
+    Status lower_row_slices() {
+        auto give_up = [&] {
+            slice_rows_ = 0;
+            slicing_ = RowSlicing{};
+            return Status();
+        };
+        Result<Graph> sliced = with_leading_extent(graph_, slicing_, slice_rows_);
+        if (!sliced.ok()) return give_up();
+        Result<LoweredGraph> lowered = lower_graph(*sliced, options_, device_.sm_count, false);
+        if (!lowered.ok()) return give_up();
+        if (lowered->steps.size() != lowered_.steps.size() || lowered->needs != lowered_.needs) return give_up();
+        for (std::size_t i = 0; i < lowered_.steps.size(); ++i) {
+            Step& mine = lowered->steps[i];
+            const Step& full = lowered_.steps[i];
+            if (mine.kind != full.kind || mine.result != full.result || mine.inputs != full.inputs ||
+                mine.write_f32 != full.write_f32 || mine.write_half != full.write_half ||
+                mine.has_epilogue != full.has_epilogue || mine.row_outputs != full.row_outputs ||
+                lowered->after_step[i].size() != lowered_.after_step[i].size()) {
+                return give_up();
+            }
+            if (mine.kind == Step::Kind::Matmul) {
+                mine.splits = full.splits;
+                if (mine.splits > 1) {
+                    lowered->workspace_bytes = std::max(
+                        lowered->workspace_bytes, static_cast<std::size_t>(mine.splits) * mine.m * mine.n * sizeof(float));
+                }
+            }
+        }
+        // Forms of cut values that a slice cannot address by rows.
+        for (std::size_t i = 0; i < graph_.num_nodes(); ++i) {
+            if (slicing_.carries[i] && (lowered_.needs[i][kRepHalfT] || lowered_.needs[i][kRepF32T])) return give_up();
+        }
+        slice_graph_ = std::move(sliced).value();
+        slice_lowered_ = std::move(lowered).value();
+        return Status();
+    }
+
+    Status add_elementwise(const Graph& graph, const Step& step, LaunchList& list) {
+        const Node& node = graph.node(step.result);
         std::vector<Shape> shapes;
-        for (NodeId in : step.inputs) shapes.push_back(graph_.node(in).type.shape);
+        for (NodeId in : step.inputs) shapes.push_back(graph.node(in).type.shape);
         ElementwiseOptions eo;
         eo.allow_vectorize = options_.vectorize;
         eo.unroll = options_.eltwise_unroll;
@@ -597,26 +823,29 @@ private:
         if (kernel.has_f32_out) {
             launch->pointers.push_back(address(step.result, kRepF32));
             launch->advances.push_back(1);
+            launch->row_bytes.push_back(row_bytes(graph, step.result, kRepF32));
         }
         if (kernel.has_half_out) {
             launch->pointers.push_back(address(step.result, kRepHalf));
             launch->advances.push_back(1);
+            launch->row_bytes.push_back(row_bytes(graph, step.result, kRepHalf));
         }
         for (NodeId in : step.inputs) {
             launch->pointers.push_back(address(in, kRepF32));
-            launch->advances.push_back(graph_.node(in).type.num_elements() == n ? 1 : 0);
+            launch->advances.push_back(graph.node(in).type.num_elements() == n ? 1 : 0);
+            launch->row_bytes.push_back(row_bytes(graph, in, kRepF32));
         }
         for (void*& p : launch->pointers) launch->params.push_back(&p);
         launch->params.push_back(&launch->count);
-        launches_.push_back(std::move(launch));
+        list.push_back(std::move(launch));
         return Status();
     }
 
     // A row reduction with its elementwise prologue: one generated kernel, a warp or a block per row.
-    Status add_reduce(const Step& step) {
-        const Node& node = graph_.node(step.result);
+    Status add_reduce(const Graph& graph, const Step& step, LaunchList& list) {
+        const Node& node = graph.node(step.result);
         std::vector<Shape> shapes;
-        for (NodeId in : step.inputs) shapes.push_back(graph_.node(in).type.shape);
+        for (NodeId in : step.inputs) shapes.push_back(graph.node(in).type.shape);
         const RowReduceKernel kernel = generate_row_reduce_kernel(step.reduce_op, step.program, shapes, step.reduce_shape);
 
         auto launch = std::make_unique<Launch>();
@@ -640,25 +869,27 @@ private:
         launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(wanted, resident)));
         launch->pointers.push_back(address(step.result, kRepF32));
         launch->advances.push_back(0);
+        launch->row_bytes.push_back(row_bytes(graph, step.result, kRepF32));
         for (NodeId in : step.inputs) {
             launch->pointers.push_back(address(in, kRepF32));
             launch->advances.push_back(0);
+            launch->row_bytes.push_back(row_bytes(graph, in, kRepF32));
         }
         for (void*& p : launch->pointers) launch->params.push_back(&p);
         launch->params.push_back(&launch->count);
-        launches_.push_back(std::move(launch));
+        list.push_back(std::move(launch));
         return Status();
     }
 
     // A run of steps on rows of one shape as one kernel, a block per row.
-    Status add_row_fused(const Step& step) {
+    Status add_row_fused(const Graph& graph, const Step& step, LaunchList& list) {
         const std::string source = generate_row_fused_kernel(step.row_parts, step.row_externals,
                                                              static_cast<int>(step.row_outputs.size()), step.reduce_shape.back());
         auto launch = std::make_unique<Launch>();
         launch->kind = Launch::Kind::Elementwise;
         double ms = 0.0;
         if (mcd_jit_kernel(options_.device, source.c_str(), kRowFusedKernelName, "--fmad=false", &launch->function, &ms) != 0) {
-            return Error{std::string("compiling the row kernel of '") + graph_.node(step.result).name + "' failed: " + mcd_last_error()};
+            return Error{std::string("compiling the row kernel of '") + graph.node(step.result).name + "' failed: " + mcd_last_error()};
         }
         jit_ms_ += ms;
         jit_functions_.push_back(launch->function);
@@ -676,18 +907,20 @@ private:
         for (NodeId w : step.row_outputs) {
             launch->pointers.push_back(address(w, kRepF32));
             launch->advances.push_back(0);
+            launch->row_bytes.push_back(row_bytes(graph, w, kRepF32));
         }
         for (NodeId in : step.inputs) {
             launch->pointers.push_back(address(in, kRepF32));
             launch->advances.push_back(0);
+            launch->row_bytes.push_back(row_bytes(graph, in, kRepF32));
         }
         for (void*& p : launch->pointers) launch->params.push_back(&p);
         launch->params.push_back(&launch->count);
-        launches_.push_back(std::move(launch));
+        list.push_back(std::move(launch));
         return Status();
     }
 
-    Status add_matmul(const Step& step, float* workspace) {
+    Status add_matmul(const Graph& graph, const Step& step, float* workspace, LaunchList& list) {
         auto launch = std::make_unique<Launch>();
         launch->kind = Launch::Kind::Matmul;
         launch->reported = step.kernel;
@@ -719,6 +952,10 @@ private:
             g.c16_kind = step.write_half == HalfKind::Bf16 ? MCD_HALF_BF16 : MCD_HALF_F16;
             g.ldc16 = half_pitch(step.n);
         }
+        std::vector<std::size_t> epilogue_row_bytes;
+        launch->row_bytes = {row_bytes(graph, step.lhs, half ? kRepHalf : kRepF32),
+                             step.write_f32 ? row_bytes(graph, step.result, kRepF32) : 0,
+                             step.write_half != HalfKind::None ? row_bytes(graph, step.result, kRepHalf) : 0};
         g.splits = step.splits;
         g.tile_n = step.tile_n;
         g.workspace = step.splits > 1 ? workspace : nullptr;
@@ -733,9 +970,10 @@ private:
             for (std::size_t k = 0; k < step.inputs.size(); ++k) {
                 if (step.load_is_accumulator[k]) continue;
                 g.epilogue_inputs[slot++] = reinterpret_cast<const float*>(address(step.inputs[k], kRepF32));
+                epilogue_row_bytes.push_back(row_bytes(graph, step.inputs[k], kRepF32));
             }
             g.num_epilogue_inputs = slot;
-            const std::string epilogue = generate_epilogue_source(graph_, step);
+            const std::string epilogue = generate_epilogue_source(graph, step);
             sources_.push_back(epilogue);
             double ms = 0.0;
             if (mcd_gemm_launches(&g) > 1) {
@@ -743,7 +981,7 @@ private:
                 const std::string source = epilogue + mcd_gemm_source(-1);
                 if (mcd_jit_kernel(options_.device, source.c_str(), mcd_gemm_entry_point(nullptr), "--fmad=false",
                                    &g.reduce_function, &ms) != 0) {
-                    return Error{std::string("compiling the epilogue of '") + graph_.node(step.result).name +
+                    return Error{std::string("compiling the epilogue of '") + graph.node(step.result).name +
                                  "' failed: " + mcd_last_error()};
                 }
                 jit_functions_.push_back(g.reduce_function);
@@ -754,7 +992,7 @@ private:
                     "#define MC_SINGLE_ENTRY 1\n#define MC_ONLY_" + entry + " 1\n" + epilogue + mcd_gemm_source(g.arith);
                 if (mcd_jit_kernel(options_.device, source.c_str(), entry.c_str(), "--fmad=false", &g.function,
                                    &ms) != 0) {
-                    return Error{std::string("compiling the epilogue of '") + graph_.node(step.result).name +
+                    return Error{std::string("compiling the epilogue of '") + graph.node(step.result).name +
                                  "' failed: " + mcd_last_error()};
                 }
                 jit_functions_.push_back(g.function);
@@ -763,7 +1001,8 @@ private:
             }
             jit_ms_ += ms;
         }
-        launches_.push_back(std::move(launch));
+        launch->row_bytes.insert(launch->row_bytes.end(), epilogue_row_bytes.begin(), epilogue_row_bytes.end());
+        list.push_back(std::move(launch));
         return Status();
     }
 
@@ -790,7 +1029,17 @@ private:
     std::size_t status_offset_ = 0;
     bool uses_status_ = false;
     std::vector<std::size_t> offset_;  // per (node, rep): byte offset in the arena
-    std::vector<std::unique_ptr<Launch>> launches_;
+    LaunchList launches_;
+    // Row slicing of run() on pinned memory: the analysis, the rows per slice (0 = off), the graph and plan at
+    // that row count, and its launches, which use the full plan's addresses and are moved row-wise per slice.
+    static constexpr std::size_t kMinSlicedBytes = std::size_t{32} << 20;
+    RowSlicing slicing_;
+    std::int64_t slice_rows_ = 0;
+    Graph slice_graph_;
+    LoweredGraph slice_lowered_;
+    LaunchList slice_launches_;
+    std::vector<Launch> slice_upload_recasts_;
+    std::size_t unpooled_output_bytes_ = 0;
     std::vector<Launch> upload_recasts_;
     std::vector<Launch> constant_recasts_;
     std::vector<std::string> sources_;

@@ -90,6 +90,8 @@ public:
     // Device address of the word into which a tensor-core kernel that gives up a bounded wait ORs its code
     // (nullptr when no launch of this executable can wait). synchronize() / download_outputs() read and clear it.
     virtual void* status_word_address() const = 0;
+    // Row slices run() on pinned host memory is cut into (0: it copies in, runs and copies out, or streams).
+    virtual std::size_t row_slices() const = 0;
     virtual std::size_t arena_bytes() const = 0;
     virtual std::string plan_description() const = 0;
     // Device address and element count of output k's FP32 buffer.

@@ -377,7 +377,7 @@ void rematerialize_for_reductions(const Graph& graph, std::vector<Step>* steps) 
 
 }  // namespace
 
-Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options, int sm_count) {
+Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options, int sm_count, bool pool_outputs) {
     const std::size_t count = graph.num_nodes();
     const std::vector<std::vector<NodeId>> users = graph.compute_users();
     LoweredGraph out;
@@ -594,8 +594,8 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
         for (int rep = 0; rep < kNumReps; ++rep) {
             PoolValue& v = out.pool_values[i * kNumReps + static_cast<std::size_t>(rep)];
             v.bytes = rep_bytes(n.type, static_cast<Rep>(rep));
-            v.pooled = is_compute(n.op) && out.needs[i][static_cast<std::size_t>(rep)];
             v.live_out = rep == kRepF32 && graph.is_output(static_cast<NodeId>(i));
+            v.pooled = is_compute(n.op) && out.needs[i][static_cast<std::size_t>(rep)] && (pool_outputs || !v.live_out);
         }
     }
     auto value_index = [](NodeId node, Rep rep) { return static_cast<std::int32_t>(node) * kNumReps + rep; };

@@ -83,7 +83,8 @@ struct CudaOptions {
     // kernels) - on B200 the 512 MiB GELU pass streams at 6.32 TB/s this way. n > 0: one wave of n looping blocks per
     // SM instead (4 was the best of those at 5.94 TB/s; 3 gives 5.43, 5 gives 5.46, 8 gives 5.36).
     int eltwise_blocks_per_sm = 0;
-    int host_io_slices = 10;    // slices of the pipelined run() on pinned host memory (host_io = 1)
+    int host_io_slices = 10;    // slices of the pipelined run() on pinned host memory (host_io = 1), streaming graphs
+    int host_io_row_slices = 16;  // same for row-independent graphs with matmuls or row kernels (0 turns that path off)
     bool fuse_rows = true;      // runs of steps on rows of one shape become one kernel (reduce_codegen.hpp)
     bool rematerialize = true;  // recompute cheap elementwise values read by a row reduction in each reader
 };
@@ -167,7 +168,10 @@ struct LoweredGraph {
 inline std::int64_t half_pitch(std::int64_t cols) { return (cols + 7) / 8 * 8; }
 std::size_t rep_bytes(const TensorType& type, Rep rep);
 
-Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options, int sm_count);
+// pool_outputs = false keeps the FP32 form of every graph output out of the buffer pool (the executable then gives
+// each output a region of its own): needed when row slices of one run overlap, so that a later slice's
+// intermediates cannot land on an earlier slice's output rows that are still being copied out.
+Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options, int sm_count, bool pool_outputs = true);
 
 // The `mc_epilogue` device function for a matmul step with a folded consumer
 // (the text that goes in front of mcd_gemm_source()).

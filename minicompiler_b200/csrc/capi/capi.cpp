@@ -5,6 +5,7 @@
 
 #include "backend/b200_backend.hpp"
 #include "backend/partition.hpp"
+#include "backend/row_slicing.hpp"
 #include "core/passes.hpp"
 #include "core/plan.hpp"
 #include "minicompiler_b200_device.h"
@@ -117,6 +118,8 @@ Status parse_options(const char* text, cuda::CudaOptions* options) {
                 options->gemm_variant = static_cast<int>(number);
             } else if (key == "host_io_slices") {
                 options->host_io_slices = static_cast<int>(number);
+            } else if (key == "host_io_row_slices") {
+                options->host_io_row_slices = static_cast<int>(number);
             } else if (key == "fuse_rows") {
                 options->fuse_rows = number != 0;
             } else if (key == "rematerialize") {
@@ -131,7 +134,7 @@ Status parse_options(const char* text, cuda::CudaOptions* options) {
                 options->eltwise_blocks_per_sm = static_cast<int>(number);
             } else {
                 return Error{"unknown option '" + key +
-                             "' (device, matmul, vectorize, fuse_epilogue, b_layout, unroll, streaming, gemm_variant, fmad, blocks_per_sm, graph, host_io, host_io_slices, rematerialize, fuse_rows)"};
+                             "' (device, matmul, vectorize, fuse_epilogue, b_layout, unroll, streaming, gemm_variant, fmad, blocks_per_sm, graph, host_io, host_io_slices, host_io_row_slices, rematerialize, fuse_rows)"};
             }
         }
     }
@@ -329,6 +332,11 @@ int mcb_in_place_pointers_ok(const void* const* pointers, int count, int any_vec
     return minicompiler::cuda::in_place_pointers_ok(any_vectorized != 0, list) ? 1 : 0;
 }
 
+int mc_row_slices(void* handle) {
+    Compiled* c = as_compiled(handle);
+    return c->gpu != nullptr ? static_cast<int>(c->gpu->row_slices()) : 0;
+}
+
 int mc_refresh_constants(void* handle) {
     Compiled* c = as_compiled(handle);
     return c->gpu != nullptr ? failed(c->gpu->refresh_constants()) : 1;
@@ -451,6 +459,28 @@ int mcb_graph_fusion_groups(const void* graph, char* out, int size) {
         std::string line;
         for (NodeId m : group) line += (line.empty() ? "" : " ") + g.node(m).name;
         text += line + "\n";
+    }
+    return put_len(out, size, text);
+}
+
+int mcb_graph_row_slicing(const void* graph, long long slice_rows, char* out, int size) {
+    const Graph& g = static_cast<const OpenGraph*>(graph)->graph;
+    const cuda::RowSlicing slicing = cuda::analyze_row_slicing(g);
+    if (!slicing.ok) return put_len(out, size, "none");
+    std::string text = "rows=" + std::to_string(slicing.rows) + " cut=";
+    bool first = true;
+    for (std::size_t i = 0; i < g.num_nodes(); ++i) {
+        if (!slicing.carries[i]) continue;
+        text += (first ? "" : ",") + g.node(static_cast<NodeId>(i)).name;
+        first = false;
+    }
+    if (slice_rows > 0) {
+        Result<Graph> sliced = cuda::with_leading_extent(g, slicing, slice_rows);
+        if (!sliced.ok()) {
+            g_error = sliced.error().message;
+            return -1;
+        }
+        text += "\n" + print_graph(*sliced);
     }
     return put_len(out, size, text);
 }

@@ -229,21 +229,25 @@ def test_two_shards_on_the_device_reproduce_the_unsharded_rows(mc, oracle, name,
     g = oracle.parse_mcg_file(path, dims)
     shape = g.node(g.inputs[0]).shape
     x = oracle.normal_values(int(np.prod(shape)), 9).reshape(shape)
+    def k_splits(d):
+        plan = mc.HostGraph(path, dims=d).launch_plan({"matmul": matmul})
+        return re.findall(r"splits=(\d+)", plan)
+
     with mc.CompiledGraph(path, dims=dims, options={"matmul": matmul}) as exe:
         whole = exe.run([x])[0].reshape(shape[0], -1)
-        whole_launches = exe.kernel_launches
-    parts, part_launches = [], None
+    parts, same_splits = [], True
     for rank in range(2):
         shard, first, rows = mc.shard_dims(path, dims, lead, rank, 2)
         assert (first, rows) == (rank * shape[0] // 2, shape[0] // 2)
+        same_splits = same_splits and k_splits(shard) == k_splits(dims)
         with mc.CompiledGraph(path, dims=shard, options={"matmul": matmul}) as exe:
             parts.append(exe.run([x[first:first + rows]])[0].reshape(rows, -1))
-            part_launches = exe.kernel_launches
     halves = np.concatenate(parts)
-    if part_launches == whole_launches:  # same number of launches: no matmul gained or lost a K split
+    if same_splits:
         assert np.array_equal(halves, whole), f"{name} {matmul}: shards differ from the unsharded run"
-    else:
+    else:  # a different K split adds the same FP32 products in another order
         err = nse(halves, whole)
+        print(f"\n{name} {matmul}: the shards split K differently; they differ from the unsharded run by {err:.3e}")
         assert err <= TOL[matmul] * 1e-2, f"{name} {matmul}: shards differ from the unsharded run by {err:.3e}"
 
 
@@ -318,3 +322,56 @@ def test_softmax_and_layernorm_against_torch_float64(mc, oracle):
             want = torch.nn.functional.layer_norm(t, (dims["N"],), torch.from_numpy(gamma), torch.from_numpy(beta), eps).numpy()
         err = nse(got, want)
         assert err <= 1e-5, f"{name} {dims}: {err:.2e} against torch float64"
+
+
+# ------------------------------------------ mc_run on pinned memory in overlapping row slices
+
+
+@pytest.mark.parametrize("name,dims,matmul", [
+    ("c5_mlp_stack", {"B": 8192, "D": 1024}, "tensor_core_f16"),
+    ("c5_mlp_stack", {"B": 4096, "D": 1024}, "tensor_core_bf16"),
+    ("c3_ffn", {"T": 4096, "D": 1024, "H": 4096}, "tensor_core_tf32"),
+    ("c3_ffn", {"T": 4096, "D": 1024, "H": 2048}, "auto"),
+    ("c1_mlp_block", {"B": 16384}, "auto"),
+    ("c4_matmul", {"M": 8192, "N": 2048, "K": 512}, "tensor_core_bf16"),
+    ("x1_softmax", {"M": 4096, "N": 4096}, "auto"),
+])
+def test_run_in_row_slices_on_pinned_memory_is_bit_identical(mc, oracle, name, dims, matmul):
+    """On pinned buffers mc_run cuts a row-independent graph into slices whose copy-in, kernels and copy-out overlap.
+    The result must be, bit for bit, what the plain copy-in / run / copy-out path gives (host_io=0), twice in a row
+    (the second call reuses buffers the first one left dirty), and the pageable-memory path must agree too."""
+    import torch
+
+    path = mc.graph_path(name)
+    g = oracle.parse_mcg_file(path, dims)
+    ins = [fast_normal(int(np.prod(g.node(n).shape)), 40 + k) for k, n in enumerate(g.inputs)]
+    with mc.CompiledGraph(path, dims=dims, options={"matmul": matmul, "host_io": 0}) as exe:
+        assert exe.row_slices == 0
+        want = exe.run(ins)[0]
+    pins = [torch.from_numpy(a).pin_memory() for a in ins]
+    out = torch.full((want.size,), float("nan"), dtype=torch.float32).pin_memory()
+    with mc.CompiledGraph(path, dims=dims, options={"matmul": matmul}) as exe:
+        assert exe.row_slices >= 2, "this graph should run in row slices"
+        for _ in range(2):
+            exe.run_ptrs([p.data_ptr() for p in pins], [out.data_ptr()])
+            assert np.array_equal(out.numpy(), want), f"{name} {matmul}: sliced run differs from the plain run"
+            out.fill_(float("nan"))
+        assert np.array_equal(exe.run(ins)[0], want)  # pageable buffers: plain path of the same executable
+        exe.upload(ins)
+        exe.enqueue()
+        assert np.array_equal(exe.download()[0], want)  # and the unsliced launch list still works beside it
+    with mc.CompiledGraph(path, dims=dims, options={"matmul": matmul, "host_io_row_slices": 5}) as exe:
+        # a slice count that does not divide the rows into whole tiles is lowered to one that does
+        assert exe.row_slices in (0, 2, 4)
+        exe.run_ptrs([p.data_ptr() for p in pins], [out.data_ptr()])
+        assert np.array_equal(out.numpy(), want)
+
+
+def test_small_or_row_dependent_graphs_are_not_sliced(mc):
+    with mc.CompiledGraph(mc.graph_path("c5_mlp_stack"), dims={"B": 256, "D": 256}, options={"matmul": "tensor_core_f16"}) as exe:
+        assert exe.row_slices == 0  # moves too little for the overlap to pay
+    with mc.CompiledGraph(mc.graph_path("c2_gelu_chain"), dims={"M": 4096, "N": 4096}) as exe:
+        assert exe.row_slices == 0  # one streaming kernel: it has its own pipeline
+    text = "input x : f32[4096, 4096]\nz = matmul x, x\noutput z"
+    with mc.CompiledGraph(text=text, options={"matmul": "tensor_core_bf16"}) as exe:
+        assert exe.row_slices == 0

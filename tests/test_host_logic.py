@@ -598,3 +598,33 @@ def test_no_tensor_can_outgrow_the_32_bit_indices_of_the_generated_kernels(mc):
     fine = "input x : f32[32768, 65535]\ny = exp x\ns = row_sum y\noutput s"
     plan = mc.HostGraph(text=fine, passes="none").launch_plan()
     assert plan.strip()
+
+
+def test_row_slicing_analysis(mc):
+    """Which values mc_run may cut by rows so that the copy-in, kernels and copy-out of consecutive slices overlap:
+    a dataflow analysis over the optimized graph (the executable no longer has the source text)."""
+    def slicing(text=None, path=None, dims=None, passes="default"):
+        return mc.HostGraph(path, text=text, dims=dims, passes=passes).row_slicing()
+
+    assert slicing(path=mc.graph_path("c5_mlp_stack"), dims={"B": 1024, "D": 256}).startswith("rows=1024 cut=x,z0,a0,")
+    assert slicing(path=mc.graph_path("c3_ffn"), dims={"T": 512, "D": 128, "H": 256}) == "rows=512 cut=x,z,h,o,y"
+    # square sweep shapes: both inputs have the leading extent, only the left operand can be cut
+    assert slicing(path=mc.graph_path("c4_matmul"), dims={"M": 512, "N": 512, "K": 512}) == "rows=512 cut=a,c"
+    assert slicing(path=mc.graph_path("x1_softmax"), dims={"M": 64, "N": 256}).startswith("rows=64 cut=x,")
+    # a per-row column is cut together with the tensor it scales
+    col = "input x : f32[8, 4]\ninput s : f32[8, 1]\nconst w : f32[4, 6] = uniform(seed=1, lo=-1, hi=1)\ny = mul x, s\nz = matmul y, w\noutput z"
+    assert slicing(col, passes="none") == "rows=8 cut=x,s,y,z"
+    # rows of a right-hand side are summed over: nothing to cut
+    assert slicing("input x : f32[8, 8]\nz = matmul x, x\noutput z", passes="none") == "none"
+    # a full-height constant would need its own rows per slice
+    full = "input x : f32[8, 4]\nconst c : f32[8, 4] = uniform(seed=2, lo=-1, hi=1)\ny = add x, c\noutput y"
+    assert slicing(full, passes="none") == "none"
+    # an output that is not computed from cut values
+    assert slicing("input x : f32[8, 4]\nconst c : f32[4] = [1, 2, 3, 4]\ny = exp x\nd = exp c\noutput y, d", passes="none") == "none"
+    # a lower-rank operand aligned to the right is fine; a cut operand of lower rank than the result is not
+    assert slicing("input x : f32[8, 4]\ninput r : f32[4]\ny = add x, r\noutput y", passes="none") == "rows=8 cut=x,y"
+    assert slicing("input x : f32[8, 4]\ninput t : f32[2, 8, 4]\ny = add x, t\noutput y", passes="none") == "none"
+    # the graph at a slice's row count keeps node order and every other extent
+    sliced = mc.HostGraph(mc.graph_path("c3_ffn"), dims={"T": 512, "D": 128, "H": 256}).row_slicing(128)
+    assert "x = input : f32[128,128]" in sliced and "w1 = const <32768 values> : f32[128,256]" in sliced
+    assert "y = fused %7, %4, %0 : f32[128,128]  (output)" in sliced
