@@ -276,6 +276,17 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
+    comm_box = []
+
+    def library_comm():
+        """The library's own NCCL communicator (mcd_nccl_*): rank 0 makes the unique id, torch.distributed carries
+        its 128 bytes to the others."""
+        if not comm_box:
+            uid = [mc.Communicator.unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(uid, src=0)
+            comm_box.append(mc.Communicator(world, rank, uid[0], local_rank, timeout_s=120.0))
+        return comm_box[0]
+
     def measure(workload, steps, warmup, with_e2e, with_cpu):
         name, dims, matmul, batch_dim, kind, dist_name = WORKLOADS[workload]
         if args.dims and workload == args.workload:
@@ -291,16 +302,10 @@ def main():
             compile_options |= dict(kv.split("=") for kv in args.options.split(","))
         exe = mc.CompiledGraph(path, dims=my_dims, options=compile_options)
         if world > 1:
-            # Constants are generated identically on every rank; one NCCL broadcast over NVLink makes rank 0's
-            # copy the one everybody uses (and is the only collective on this path).
-            ptr, nbytes = exe.constants_region()
-            if nbytes > 0:
-                class _Mem:
-                    __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
-                region = torch.as_tensor(_Mem(), device=torch.device("cuda", local_rank))
-                dist.broadcast(region, src=0)
-                torch.cuda.synchronize()
-                exe.refresh_constants()
+            # Constants are generated identically on every rank; one NCCL broadcast over NVLink, issued by the
+            # library on its own communicator, makes rank 0's copy the one everybody uses. It is the only
+            # collective on this path (an output is gathered only where a caller wants it assembled).
+            exe.replicate_constants(library_comm(), root=0)
         g = oracle.parse_mcg_file(path, my_dims)
         work_rank = algorithmic_work(oracle, g, kind)
         ins = make_inputs(g, dist_name, 1 + 1000 * rank)
@@ -454,6 +459,8 @@ def main():
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
+        if comm_box:
+            comm_box[0].destroy()
         dist.destroy_process_group()
 
 

@@ -82,6 +82,15 @@ MC_EXPORT const char* mc_last_error(void);
  * replicate them; after overwriting the range call mc_refresh_constants. */
 MC_EXPORT int mc_constants_region(void* handle, void** device_ptr, size_t* bytes);
 MC_EXPORT int mc_refresh_constants(void* handle);
+/* The same two steps done by the library: one NCCL broadcast of `root`'s constants to every rank of `comm`
+ * (a handle from mcd_nccl_init, include/minicompiler_b200_device.h) followed by mc_refresh_constants; and an
+ * all-gather of output k, of which every rank holds its rows, into `device_dst` (world_size times the output's
+ * size, a device pointer). Both return when the data is in place. A rank that does not answer within the
+ * communicator's timeout aborts the communicator; the call then fails with a message in mc_last_error().
+ * These replace, on every rank but the root, the reference's per-constant blocking upload at load time
+ * (src/cuda/cuda_backend.cpp:237-240). */
+MC_EXPORT int mc_replicate_constants(void* handle, void* comm, int root);
+MC_EXPORT int mc_gather_output(void* handle, int k, void* comm, void* device_dst);
 /* Device address of the 32-bit status word of a compiled graph, or NULL in *device_ptr when none of its
  * kernels can wait. A tensor-core matmul that gives up a bounded wait ORs a code into it; mc_synchronize and
  * mc_download then fail with a message and clear it. Exposed so that this error path can be exercised from

@@ -102,6 +102,31 @@ MCD_API int mcd_graph_destroy(void* graph_exec);
 /* Number of kernel launches issued through this layer by the calling process. */
 MCD_API unsigned long long mcd_launch_count(void);
 
+/* ------------------------------------------------------------- collectives
+ * NCCL over NVLink for the batch-sharded multi-GPU path: one broadcast replicates the packed constants at load
+ * time, an all-gather assembles an output where the caller wants one. They take the place of the per-constant
+ * blocking upload of src/cuda/cuda_backend.cpp:237-240 on every rank but the root. libnccl.so.2 (or the file named
+ * by the environment variable MCD_NCCL_LIBRARY) is loaded at run time. Communicators are non-blocking: every call
+ * polls the communicator's state for at most `timeout_s`; a call that does not finish in time, or an asynchronous
+ * NCCL error, aborts the communicator (ncclCommAbort) and returns non-zero instead of leaving the rank hung.
+ * `comm` handles are opaque; buffers are device pointers on the communicator's device. */
+#define MCD_NCCL_ID_BYTES 128
+MCD_API int mcd_nccl_available(void);                 /* 1 when NCCL could be loaded */
+MCD_API int mcd_nccl_unique_id(char* id);             /* fills MCD_NCCL_ID_BYTES; call on one rank, share by any means */
+MCD_API int mcd_nccl_init(void** comm, int world_size, int rank, const char* id, int device, double timeout_s);
+MCD_API int mcd_nccl_broadcast(void* comm, void* buffer, size_t bytes, int root, void* stream);
+MCD_API int mcd_nccl_all_gather(void* comm, const void* send, void* recv, size_t bytes_per_rank, void* stream);
+/* Waits (bounded) until everything enqueued on `stream` has run, watching the communicator for errors. */
+MCD_API int mcd_nccl_wait(void* comm, void* stream);
+MCD_API int mcd_nccl_abort(void* comm);               /* after it every call on `comm` fails; destroy still frees it */
+MCD_API int mcd_nccl_destroy(void* comm);
+/* Host-only test hooks: replace NCCL by a stand-in that touches no GPU and no network. `failing_call` (an NCCL
+ * function name, or NULL) returns `error_code`; with stay_in_progress the stand-in never leaves the in-progress
+ * state, so the bounded polls run out. mcd_nccl_fake_aborts counts ncclCommAbort calls since installation. */
+MCD_API int mcd_nccl_install_fake(const char* failing_call, int error_code, int stay_in_progress);
+MCD_API int mcd_nccl_remove_fake(void);
+MCD_API int mcd_nccl_fake_aborts(void);
+
 /* ------------------------------------------------------- built-in kernels */
 
 /* 16-bit formats of tensor-core operands. */

@@ -10,6 +10,7 @@ otherwise. Host-only calls (parsing, passes, memory plan, kernel generation) wor
 """
 
 from .api import (  # noqa: F401
+    Communicator,
     CompiledGraph,
     HostGraph,
     McError,
@@ -25,6 +26,7 @@ from .api import (  # noqa: F401
 )
 
 __all__ = [
+    "Communicator",
     "CompiledGraph",
     "HostGraph",
     "McError",

@@ -60,6 +60,20 @@ def lib() -> C.CDLL:
         "mc_refresh_constants": (i32, [vp]),
         "mc_status_word_ptr": (i32, [vp, C.POINTER(vp)]),
         "mc_row_slices": (i32, [vp]),
+        "mc_replicate_constants": (i32, [vp, vp, i32]),
+        "mc_gather_output": (i32, [vp, i32, vp, vp]),
+        "mcd_nccl_available": (i32, []),
+        "mcd_nccl_unique_id": (i32, [cp]),
+        "mcd_nccl_init": (i32, [C.POINTER(vp), i32, i32, cp, i32, f64]),
+        "mcd_nccl_broadcast": (i32, [vp, vp, C.c_size_t, i32, vp]),
+        "mcd_nccl_all_gather": (i32, [vp, vp, vp, C.c_size_t, vp]),
+        "mcd_nccl_wait": (i32, [vp, vp]),
+        "mcd_nccl_abort": (i32, [vp]),
+        "mcd_nccl_destroy": (i32, [vp]),
+        "mcd_nccl_install_fake": (i32, [cp, i32, i32]),
+        "mcd_nccl_remove_fake": (i32, []),
+        "mcd_nccl_fake_aborts": (i32, []),
+        "mcd_last_error": (cp, []),
         "mcb_in_place_pointers_ok": (i32, [C.POINTER(vp), i32, i32]),
         "mcd_copy_h2d": (i32, [vp, vp, C.c_size_t, vp]),
         "mcd_copy_d2h": (i32, [vp, vp, C.c_size_t, vp]),
@@ -284,6 +298,16 @@ class CompiledGraph:
         """Slices mc_run cuts a call on pinned host buffers into (0: not sliced)."""
         return lib().mc_row_slices(self._h)
 
+    def replicate_constants(self, comm: "Communicator", root: int = 0) -> None:
+        """mc_replicate_constants: rank `root`'s constants become every rank's (one NCCL broadcast)."""
+        if lib().mc_replicate_constants(self._h, comm.handle, root) != 0:
+            raise McError(_last_error())
+
+    def gather_output(self, k: int, comm: "Communicator", device_dst: int) -> None:
+        """mc_gather_output: all ranks' rows of output k, in rank order, into device memory at `device_dst`."""
+        if lib().mc_gather_output(self._h, k, comm.handle, C.c_void_p(device_dst)) != 0:
+            raise McError(_last_error())
+
     def status_word_ptr(self) -> int:
         """Device address of the status word (0 when no kernel of this graph can wait)."""
         ptr = C.c_void_p()
@@ -302,6 +326,53 @@ class CompiledGraph:
         if lib().mc_output_device_ptr(self._h, k, C.byref(ptr), C.byref(n)) != 0:
             raise McError("no such output")
         return (ptr.value or 0), n.value
+
+
+class Communicator:
+    """An NCCL communicator of the device layer (mcd_nccl_*): one rank per process, one GPU per rank.
+
+    `unique_id()` is called on one rank and its 128 bytes are handed to the others by whatever means the
+    launcher offers (a torch.distributed store, MPI, a file); every rank then constructs the communicator.
+    Calls are bounded by `timeout_s`: a peer that never joins makes the call fail and aborts the communicator."""
+
+    def __init__(self, world_size: int, rank: int, unique_id: bytes, device: int, timeout_s: float = 60.0):
+        h = C.c_void_p()
+        if lib().mcd_nccl_init(C.byref(h), world_size, rank, unique_id, device, timeout_s) != 0:
+            raise McError(_device_error())
+        self.handle, self.world_size, self.rank = h, world_size, rank
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        if lib().mcd_nccl_unique_id(buf) != 0:
+            raise McError(_device_error())
+        return buf.raw
+
+    def broadcast(self, device_ptr: int, nbytes: int, root: int = 0, stream: int = 0) -> None:
+        if lib().mcd_nccl_broadcast(self.handle, C.c_void_p(device_ptr), nbytes, root, C.c_void_p(stream or None)) != 0:
+            raise McError(_device_error())
+
+    def all_gather(self, send_ptr: int, recv_ptr: int, bytes_per_rank: int, stream: int = 0) -> None:
+        if lib().mcd_nccl_all_gather(self.handle, C.c_void_p(send_ptr), C.c_void_p(recv_ptr), bytes_per_rank,
+                                     C.c_void_p(stream or None)) != 0:
+            raise McError(_device_error())
+
+    def wait(self, stream: int = 0) -> None:
+        if lib().mcd_nccl_wait(self.handle, C.c_void_p(stream or None)) != 0:
+            raise McError(_device_error())
+
+    def abort(self) -> None:
+        lib().mcd_nccl_abort(self.handle)
+
+    def destroy(self) -> None:
+        if getattr(self, "handle", None):
+            lib().mcd_nccl_destroy(self.handle)
+            self.handle = None
+
+
+def _device_error() -> str:
+    msg = lib().mcd_last_error()
+    return msg.decode() if msg else ""
 
 
 def compile_graph(path: Optional[str] = None, **kw) -> CompiledGraph:

@@ -198,6 +198,25 @@ public:
 
     void* status_word_address() const override { return uses_status_ ? status_word() : nullptr; }
 
+    Status replicate_constants(void* comm, int root) override {
+        MCD_TRY(mcd_set_device(options_.device));
+        if (constants_bytes_ == 0) return Status();
+        MCD_TRY(mcd_nccl_broadcast(comm, arena_, constants_bytes_, root, stream_));
+        MCD_TRY(mcd_nccl_wait(comm, stream_));
+        return refresh_constants();
+    }
+
+    Status gather_output(std::size_t k, void* comm, void* device_dst) override {
+        if (k >= graph_.outputs().size()) return Error{"no output " + std::to_string(k)};
+        MCD_TRY(mcd_set_device(options_.device));
+        MCD_TRY(mcd_device_synchronize());  // the kernels may sit on a caller's stream
+        MC_TRY(check_status_word());
+        const NodeId id = graph_.outputs()[k];
+        MCD_TRY(mcd_nccl_all_gather(comm, address(id, kRepF32), device_dst, graph_.node(id).type.size_bytes(), stream_));
+        MCD_TRY(mcd_nccl_wait(comm, stream_));
+        return Status();
+    }
+
     std::size_t row_slices() const override { return slice_rows_ > 0 ? static_cast<std::size_t>(slicing_.rows / slice_rows_) : 0; }
     std::size_t arena_bytes() const override { return arena_bytes_; }
     std::string plan_description() const override { return describe(graph_, lowered_); }

@@ -92,6 +92,11 @@ public:
     virtual void* status_word_address() const = 0;
     // Row slices run() on pinned host memory is cut into (0: it copies in, runs and copies out, or streams).
     virtual std::size_t row_slices() const = 0;
+    // Multi-GPU (one process per GPU, `comm` from mcd_nccl_init): one broadcast makes `root`'s packed constants
+    // everybody's and the derived forms are rebuilt; an all-gather assembles output k of all ranks (each holding
+    // its rows) in `device_dst`, world_size times the output's size. Both return when the data is in place.
+    virtual Status replicate_constants(void* comm, int root) = 0;
+    virtual Status gather_output(std::size_t k, void* comm, void* device_dst) = 0;
     virtual std::size_t arena_bytes() const = 0;
     virtual std::string plan_description() const = 0;
     // Device address and element count of output k's FP32 buffer.

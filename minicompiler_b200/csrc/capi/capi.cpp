@@ -332,6 +332,24 @@ int mcb_in_place_pointers_ok(const void* const* pointers, int count, int any_vec
     return minicompiler::cuda::in_place_pointers_ok(any_vectorized != 0, list) ? 1 : 0;
 }
 
+int mc_replicate_constants(void* handle, void* comm, int root) {
+    Compiled* c = as_compiled(handle);
+    if (c == nullptr || c->gpu == nullptr) {
+        g_error = "mc_replicate_constants: not a GPU executable";
+        return 1;
+    }
+    return failed(c->gpu->replicate_constants(comm, root));
+}
+
+int mc_gather_output(void* handle, int k, void* comm, void* device_dst) {
+    Compiled* c = as_compiled(handle);
+    if (c == nullptr || c->gpu == nullptr || k < 0) {
+        g_error = "mc_gather_output: not a GPU executable, or a negative output index";
+        return 1;
+    }
+    return failed(c->gpu->gather_output(static_cast<std::size_t>(k), comm, device_dst));
+}
+
 int mc_row_slices(void* handle) {
     Compiled* c = as_compiled(handle);
     return c->gpu != nullptr ? static_cast<int>(c->gpu->row_slices()) : 0;

@@ -375,3 +375,31 @@ def test_small_or_row_dependent_graphs_are_not_sliced(mc):
     text = "input x : f32[4096, 4096]\nz = matmul x, x\noutput z"
     with mc.CompiledGraph(text=text, options={"matmul": "tensor_core_bf16"}) as exe:
         assert exe.row_slices == 0
+
+
+# ------------------------------------------------------- collectives through the library
+
+
+def test_replicate_constants_and_gather_output_on_a_one_rank_communicator(mc, oracle):
+    """The library's own NCCL calls on real NCCL with a world of one (all a single GPU offers): the broadcast leaves
+    the constants as they were and rebuilds their 16-bit forms, the all-gather delivers the output."""
+    import torch
+
+    if not mc.lib().mcd_nccl_available():
+        pytest.skip("libnccl.so.2 cannot be loaded on this machine")
+    dims = {"B": 256, "D": 256}
+    path = mc.graph_path("c5_mlp_stack")
+    x = oracle.normal_values(256 * 256, 1)
+    comm = mc.Communicator(1, 0, mc.Communicator.unique_id(), device=0, timeout_s=60.0)
+    try:
+        with mc.CompiledGraph(path, dims=dims, options={"matmul": "tensor_core_f16"}) as exe:
+            want = exe.run([x])[0]
+            exe.replicate_constants(comm, root=0)
+            assert np.array_equal(exe.run([x])[0], want)
+            dst = torch.full((want.size,), float("nan"), dtype=torch.float32, device="cuda")
+            exe.gather_output(0, comm, dst.data_ptr())
+            assert np.array_equal(dst.cpu().numpy(), want)
+            with pytest.raises(mc.McError, match="no output 3"):
+                exe.gather_output(3, comm, dst.data_ptr())
+    finally:
+        comm.destroy()
