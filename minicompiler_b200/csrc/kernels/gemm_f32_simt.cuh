@@ -16,6 +16,21 @@
 #define MC_F32_BK 16
 #define MC_F32_APITCH 132
 
+// Two IEEE FP32 fused multiply-adds in one instruction (sm_100: fma.rn.f32x2 on register pairs). Each half is
+// rounded exactly like fmaf, so results are bit-identical to the scalar form; what changes is that a warp issues
+// half as many FMA instructions, which leaves issue slots for the shared-memory loads beside them.
+__device__ __forceinline__ unsigned long long mc_pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void mc_unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void mc_fma2(unsigned long long& acc, unsigned long long a, unsigned long long b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+
 template <bool kVec>
 __device__ __forceinline__ void mc_gemm_f32_body(const float* __restrict__ A, const float* __restrict__ B,
                                                  float* __restrict__ C, unsigned short* __restrict__ C16, int c16_kind,
@@ -94,11 +109,12 @@ __device__ __forceinline__ void mc_gemm_f32_body(const float* __restrict__ A, co
 
     const int ty = tid >> 4;  // 0..15 -> rows ty*4 and 64 + ty*4
     const int tx = tid & 15;  // 0..15 -> cols tx*4 and 64 + tx*4
-    float acc[8][8];
+    // acc2[i][p] holds columns 2p and 2p+1 of row i of the thread's 8x8 block.
+    unsigned long long acc2[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+        for (int p = 0; p < 4; ++p) acc2[i][p] = 0ull;  // two +0.0f
     }
 
     const int steps = (k_end - k_begin + MC_F32_BK - 1) / MC_F32_BK;
@@ -117,15 +133,24 @@ __device__ __forceinline__ void mc_gemm_f32_body(const float* __restrict__ A, co
             const float4 b_lo = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
             const float4 b_hi = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
             const float a[8] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
-            const float b[8] = {b_lo.x, b_lo.y, b_lo.z, b_lo.w, b_hi.x, b_hi.y, b_hi.z, b_hi.w};
+            const unsigned long long b2[4] = {mc_pack2(b_lo.x, b_lo.y), mc_pack2(b_lo.z, b_lo.w), mc_pack2(b_hi.x, b_hi.y),
+                                              mc_pack2(b_hi.z, b_hi.w)};
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
+                const unsigned long long a2 = mc_pack2(a[i], a[i]);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                for (int p = 0; p < 4; ++p) mc_fma2(acc2[i][p], a2, b2[p]);
             }
         }
         if (s + 1 < steps) stash(buf ^ 1);
         __syncthreads();
+    }
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+        for (int p = 0; p < 4; ++p) mc_unpack2(acc2[i][p], acc[i][2 * p], acc[i][2 * p + 1]);
     }
 
     const bool partial = gridDim.z > 1;
