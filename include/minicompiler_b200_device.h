@@ -72,6 +72,14 @@ MCD_API int mcd_event_destroy(void* event);
 MCD_API int mcd_event_record(void* event, void* stream);
 MCD_API int mcd_stream_wait_event(void* stream, void* event); /* later work on `stream` waits for `event` */
 MCD_API int mcd_event_elapsed_ms(void* start, void* stop, float* ms); /* waits for `stop` */
+/* Records `event` as a node of the CUDA graph being captured on `stream`, so that two of them bracket kernels
+ * inside a replayed graph and their difference leaves out the host's launch cost - how the reference times a
+ * single matmul (bench/bench_cuda.cpp:445-493). */
+MCD_API int mcd_event_record_external(void* event, void* stream);
+/* Named ranges for Nsight tools (NVTX), as the reference's profile suite wraps each launch
+ * (bench/bench_cuda.cpp:860-928, nvtxRangePushA at :873). No-ops unless a tool is attached. */
+MCD_API int mcd_range_push(const char* label);
+MCD_API int mcd_range_pop(void);
 
 /* -------------------------------------------------------- run-time kernels
  * Replaces KernelCompiler::get + cuLaunchKernel + the occupancy query

@@ -78,6 +78,12 @@ def lib() -> C.CDLL:
         "mcd_copy_h2d": (i32, [vp, vp, C.c_size_t, vp]),
         "mcd_copy_d2h": (i32, [vp, vp, C.c_size_t, vp]),
         "mcd_device_synchronize": (i32, []),
+        "mcd_event_create": (i32, [C.POINTER(vp)]),
+        "mcd_event_destroy": (i32, [vp]),
+        "mcd_event_record_external": (i32, [vp, vp]),
+        "mcd_event_elapsed_ms": (i32, [vp, vp, C.POINTER(C.c_float)]),
+        "mcd_range_push": (i32, [cp]),
+        "mcd_range_pop": (i32, []),
         "mcd_jit_cache_stats": (i32, [C.POINTER(i64), C.POINTER(i64)]),
         "mcd_per_device_once_probe": (i32, [C.POINTER(i32), i32, C.POINTER(i32)]),
         "mc_input_device_ptr": (i32, [vp, i32, C.POINTER(vp), C.POINTER(C.c_size_t)]),

@@ -1,6 +1,6 @@
 """The reference's GPU benchmark suites, re-hosted on this backend (needs a B200).
 
-    python -m minicompiler_b200.bench_suites --suite elementwise|matmul|tensor_core|rows|all [--out FILE]
+    python -m minicompiler_b200.bench_suites --suite elementwise|matmul|tensor_core|rows|profile|all [--out FILE]
 
 They follow bench/bench_cuda.cpp of the reference:
   elementwise   the GELU chain at M in {1,16,256,1024,4096,16384}, N=4096, unfused (passes
@@ -10,15 +10,23 @@ They follow bench/bench_cuda.cpp of the reference:
   tensor_core   the tcgen05 kernels against cuBLAS in the same format (run_tensor_core, :700-851).
   rows          (no counterpart in the reference) softmax and LayerNorm graphs built from the row reductions
                 against torch's kernels.
+  profile       one launch of every kernel, each inside its own NVTX range "<workload>.<kernel>", nothing timed,
+                for `ncu --nvtx --nvtx-include "<label>/"` (run_profile, :860-928; `--list` prints the labels,
+                `--only LABEL` runs one).
 Every variant is checked before it is timed: 1000 sampled outputs against float64 dot products
 (the method of run_and_check, :386-436). cuBLAS is reached through torch.matmul and is a comparison
-column only, never part of the product. Times are CUDA events around `mc_enqueue` on a side stream,
-median of `--rounds` rounds, L2 flushed between rounds for working sets that fit it.
+column only, never part of the product.
+Matmul rows are timed the way the reference times them (time_graphs, :445-493): the launch is captured in a CUDA
+graph between two event-record nodes and the graph is replayed, so the time between the events leaves out the
+host's cost of launching, which differs between cuBLAS and these kernels. The elementwise and rows suites time
+CUDA events around `mc_enqueue` on a side stream. Median of `--rounds` rounds, L2 flushed between rounds for
+working sets that fit it.
 """
 
 from __future__ import annotations
 
 import argparse
+import ctypes as C
 import json
 import sys
 from pathlib import Path
@@ -49,6 +57,39 @@ def _median_ms(fn, stream, rounds, flush):
             times.append((e0, e1))
     torch.cuda.synchronize()
     return float(np.median([a.elapsed_time(b) for a, b in times]))
+
+
+def _graph_median_ms(mc, fn, stream, rounds, flush):
+    """Median time of `fn` (which enqueues on `stream`) inside a replayed CUDA graph, between two event nodes."""
+    import torch
+
+    lib = mc.lib()
+    start, stop = C.c_void_p(), C.c_void_p()
+    assert lib.mcd_event_create(C.byref(start)) == 0 and lib.mcd_event_create(C.byref(stop)) == 0
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+        assert lib.mcd_event_record_external(start, C.c_void_p(stream.cuda_stream)) == 0
+        fn()
+        assert lib.mcd_event_record_external(stop, C.c_void_p(stream.cuda_stream)) == 0
+    scrub = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    times, ms = [], C.c_float()
+    with torch.cuda.stream(stream):
+        for i in range(rounds + 3):
+            if scrub is not None:
+                scrub.fill_(i & 0xFF)
+            graph.replay()
+            assert lib.mcd_event_elapsed_ms(start, stop, C.byref(ms)) == 0  # waits for the stop event
+            if i >= 3:
+                times.append(ms.value)
+    torch.cuda.synchronize()
+    del graph
+    lib.mcd_event_destroy(start)
+    lib.mcd_event_destroy(stop)
+    return float(np.median(times))
 
 
 def _bytes_moved(mc, path, dims, passes):
@@ -136,12 +177,12 @@ def _gemm_rows(mc, rounds, shapes, kernels):
                 exe.enqueue(stream.cuda_stream)
                 got = exe.download()[0].reshape(m, n)
                 rel = _check_sampled(got, a, b, u_in, k)
-                ms = _median_ms(lambda: exe.enqueue(stream.cuda_stream), stream, rounds, small)
+                ms = _graph_median_ms(mc, lambda: exe.enqueue(stream.cuda_stream), stream, rounds, small)
                 ran = exe.matmul_kernels
             torch.backends.cuda.matmul.allow_tf32 = tf32
             xa, xb = ta.to(torch_dtype), tb.to(torch_dtype)
-            with torch.cuda.stream(stream):
-                lib_ms = _median_ms(lambda: torch.matmul(xa, xb), stream, rounds, small)
+            out = torch.empty((m, n), dtype=torch_dtype, device="cuda")
+            lib_ms = _graph_median_ms(mc, lambda: torch.matmul(xa, xb, out=out), stream, rounds, small)
             torch.backends.cuda.matmul.allow_tf32 = False
             entry[name] = {"ms": ms, "tflops": flops / ms / 1e9, "cublas_ms": lib_ms, "cublas_tflops": flops / lib_ms / 1e9,
                            "pct_of_cublas": 100.0 * lib_ms / ms, "ran": ran, "max_err_over_abs_dot": rel}
@@ -149,18 +190,18 @@ def _gemm_rows(mc, rounds, shapes, kernels):
     return rows
 
 
-def suite_matmul(mc, rounds):
+def suite_matmul(mc, rounds, shapes=None):
     import torch
 
-    shapes = [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (256, 2048, 512), (128, 512, 2048), (256, 1024, 1024),
+    shapes = shapes or [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (256, 2048, 512), (128, 512, 2048), (256, 1024, 1024),
               (8192, 4096, 1024)]
     return _gemm_rows(mc, rounds, shapes, [("auto", torch.float32, False, 0.0)])
 
 
-def suite_tensor_core(mc, rounds):
+def suite_tensor_core(mc, rounds, shapes=None):
     import torch
 
-    shapes = [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (16, 8192, 8192), (128, 8192, 8192),
+    shapes = shapes or [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (16, 8192, 8192), (128, 8192, 8192),
               (1024, 1024, 65536), (65536, 2048, 2048)]
     kernels = [("tensor_core_tf32", torch.float32, True, 2.0 ** -11), ("tensor_core_bf16", torch.bfloat16, False, 2.0 ** -8),
                ("tensor_core_f16", torch.float16, False, 2.0 ** -11)]
@@ -208,25 +249,101 @@ def suite_rows(mc, rounds):
     return rows
 
 
+PROFILE_SHAPES = [(2048, 2048, 2048), (512, 512, 512), (128, 2048, 512)]  # m, k, n: the reference's three
+PROFILE_KERNELS = ["auto", "tensor_core_tf32", "tensor_core_bf16", "tensor_core_f16"]
+
+
+def profile_labels():
+    labels = ["gelu_64MB.unfused", "gelu_64MB.fused"]
+    for m, k, n in PROFILE_SHAPES:
+        base = f"matmul_{m}x{k}x{n}"
+        labels += [f"{base}.{kernel}" for kernel in PROFILE_KERNELS]
+        labels += [f"{base}.cublas", f"{base}.cublas_tf32", f"{base}.cublas_bf16", f"{base}.cublas_f16"]
+    return labels
+
+
+def suite_profile(mc, only=""):
+    """One launch of every kernel inside its own NVTX range; each runs once outside the ranges first, so module
+    loading and first-call set-up stay out of the profile. Returns the labels that ran."""
+    import torch
+
+    lib = mc.lib()
+    stream = torch.cuda.Stream()
+    ran = []
+
+    def profiled(label, launch):
+        if only and label != only:
+            return
+        with torch.cuda.stream(stream):
+            launch()
+            torch.cuda.synchronize()
+            lib.mcd_range_push(label.encode())
+            launch()
+            torch.cuda.synchronize()
+            lib.mcd_range_pop()
+        ran.append(label)
+        print(label)
+
+    if not only or only.startswith("gelu_64MB."):
+        x = np.random.default_rng(1).standard_normal(4096 * 4096, dtype=np.float32)
+        for name, passes in (("unfused", "dne,fold,dne"), ("fused", "default")):
+            with mc.CompiledGraph(mc.graph_path("c2_gelu_chain"), dims={"M": 4096, "N": 4096}, passes=passes) as exe:
+                exe.upload([x])
+                profiled(f"gelu_64MB.{name}", lambda: exe.enqueue(stream.cuda_stream))
+    text = "dim M = 8\ndim N = 8\ndim K = 8\ninput a : f32[M, K]\ninput b : f32[K, N]\nc = matmul a, b\noutput c"
+    for m, k, n in PROFILE_SHAPES:
+        base = f"matmul_{m}x{k}x{n}"
+        if only and not only.startswith(base + "."):
+            continue
+        a = mc.uniform_values(m * k, 1, -1, 1).reshape(m, k)
+        b = mc.uniform_values(k * n, 2, -1, 1).reshape(k, n)
+        for kernel in PROFILE_KERNELS:
+            with mc.CompiledGraph(text=text, dims={"M": m, "N": n, "K": k}, options={"matmul": kernel}) as exe:
+                exe.upload([a, b])
+                profiled(f"{base}.{kernel}", lambda: exe.enqueue(stream.cuda_stream))
+        ta, tb = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+        for suffix, dtype, tf32 in (("cublas", torch.float32, False), ("cublas_tf32", torch.float32, True),
+                                    ("cublas_bf16", torch.bfloat16, False), ("cublas_f16", torch.float16, False)):
+            xa, xb = ta.to(dtype), tb.to(dtype)
+            torch.backends.cuda.matmul.allow_tf32 = tf32
+            profiled(f"{base}.{suffix}", lambda: torch.matmul(xa, xb))
+            torch.backends.cuda.matmul.allow_tf32 = False
+    return ran
+
+
+def _parse_shapes(text):
+    return [tuple(int(t) for t in item.split("x")) for item in text.split(",") if item]
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--suite", default="all", choices=["elementwise", "matmul", "tensor_core", "rows", "all"])
+    ap.add_argument("--suite", default="all", choices=["elementwise", "matmul", "tensor_core", "rows", "profile", "all"])
     ap.add_argument("--rounds", type=int, default=30)
     ap.add_argument("--out", default="")
+    ap.add_argument("--shapes", default="", help="matmul / tensor_core: MxNxK,MxNxK,... instead of the suite's own shapes")
+    ap.add_argument("--only", default="", help="profile: run this label only")
+    ap.add_argument("--list", action="store_true", help="profile: print the labels and exit (needs no GPU)")
     args = ap.parse_args()
+    if args.suite == "profile" and args.list:
+        print("\n".join(profile_labels()))
+        return
     import torch
 
     import minicompiler_b200 as mc
 
     if not torch.cuda.is_available():
         raise SystemExit("the suites need a B200")
+    if args.suite == "profile":
+        ran = suite_profile(mc, args.only)
+        print(f"profiled {len(ran)} launch(es) on {torch.cuda.get_device_name(0)}")
+        return
     result = {"device": torch.cuda.get_device_name(0)}
     if args.suite in ("elementwise", "all"):
         result["elementwise"] = suite_elementwise(mc, args.rounds)
     if args.suite in ("matmul", "all"):
-        result["matmul"] = suite_matmul(mc, args.rounds)
+        result["matmul"] = suite_matmul(mc, args.rounds, _parse_shapes(args.shapes) if args.suite == "matmul" else None)
     if args.suite in ("tensor_core", "all"):
-        result["tensor_core"] = suite_tensor_core(mc, args.rounds)
+        result["tensor_core"] = suite_tensor_core(mc, args.rounds, _parse_shapes(args.shapes) if args.suite == "tensor_core" else None)
     if args.suite in ("rows", "all"):
         result["rows"] = suite_rows(mc, args.rounds)
     text = json.dumps(result, indent=1)

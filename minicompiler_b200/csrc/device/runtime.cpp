@@ -11,6 +11,7 @@
 #include <cuda_runtime_api.h>
 #include <dlfcn.h>
 #include <nvrtc.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <atomic>
 #include <chrono>
@@ -344,6 +345,18 @@ int mcd_stream_wait_event(void* stream, void* event) {
 }
 int mcd_event_record(void* event, void* stream) {
     return check_rt(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)), "cudaEventRecord");
+}
+int mcd_event_record_external(void* event, void* stream) {
+    return check_rt(cudaEventRecordWithFlags(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream), cudaEventRecordExternal),
+                    "cudaEventRecordWithFlags(external)");
+}
+int mcd_range_push(const char* label) {
+    nvtxRangePushA(label != nullptr ? label : "");
+    return 0;
+}
+int mcd_range_pop(void) {
+    nvtxRangePop();
+    return 0;
 }
 int mcd_event_elapsed_ms(void* start, void* stop, float* ms) {
     if (int rc = check_rt(cudaEventSynchronize(static_cast<cudaEvent_t>(stop)), "cudaEventSynchronize")) return rc;

@@ -403,3 +403,25 @@ def test_replicate_constants_and_gather_output_on_a_one_rank_communicator(mc, or
                 exe.gather_output(3, comm, dst.data_ptr())
     finally:
         comm.destroy()
+
+
+# --------------------------------------------------------- the re-hosted benchmark suites
+
+
+def test_bench_suites_tensor_core_rows_and_profile_labels(mc):
+    """The tensor_core suite on two small shapes: every row was checked against float64 samples before it was timed
+    (the suite asserts the rounding bound itself), the sampled-error column stays inside each format's unit
+    roundoff, and the times come from a replayed CUDA graph. The profile suite runs one labelled launch."""
+    from minicompiler_b200 import bench_suites
+
+    rows = bench_suites.suite_tensor_core(mc, rounds=5, shapes=[(256, 256, 256), (1024, 512, 2048)])
+    assert [(r["m"], r["n"], r["k"]) for r in rows] == [(256, 256, 256), (1024, 512, 2048)]
+    for r in rows:
+        for name, unit in (("tensor_core_tf32", 2.0 ** -11), ("tensor_core_bf16", 2.0 ** -8), ("tensor_core_f16", 2.0 ** -11)):
+            col = r[name]
+            assert 0.0 < col["max_err_over_abs_dot"] <= 2.0 * unit + 1e-6, (name, col)
+            assert col["ms"] > 0 and col["cublas_ms"] > 0 and col["ran"] == [name]
+    fp32 = bench_suites.suite_matmul(mc, rounds=5, shapes=[(256, 2048, 512)])[0]["auto"]
+    assert fp32["max_err_over_abs_dot"] <= 1e-6 and fp32["ran"] == ["split_k"]
+    assert "matmul_512x512x512.tensor_core_bf16" in bench_suites.profile_labels()
+    assert bench_suites.suite_profile(mc, only="matmul_512x512x512.tensor_core_bf16") == ["matmul_512x512x512.tensor_core_bf16"]
