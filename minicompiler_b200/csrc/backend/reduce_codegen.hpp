@@ -24,10 +24,10 @@ inline constexpr const char* kRowReduceKernelName = "mc_row_reduce";
 inline constexpr unsigned kRowReduceBlock = 256;
 
 // Threads that share a row, for both kernels of this file: a warp below 1024 elements (8 rows per 256-thread
-// block), a 256-thread block up to 8192, a 512-thread block up to 16384 (so that a row still fits the registers of
-// the row-fused kernel), 256 beyond.
+// block), a 256-thread block up to 8192, 512 threads up to 16384 and 1024 up to 32768 (so that a row still fits the
+// registers of the row-fused kernel, 32 per full-shaped value and thread), 256 beyond.
 inline unsigned row_threads(std::int64_t width) {
-    return width < 1024 ? 32u : width <= 8192 ? 256u : width <= 16384 ? 512u : 256u;
+    return width < 1024 ? 32u : width <= 8192 ? 256u : width <= 16384 ? 512u : width <= 32768 ? 1024u : 256u;
 }
 inline unsigned row_block(std::int64_t width) { return row_threads(width) > kRowReduceBlock ? row_threads(width) : kRowReduceBlock; }
 
@@ -56,7 +56,7 @@ namespace minicompiler::cuda {
 
 inline constexpr const char* kRowFusedKernelName = "mc_row_fused";
 inline constexpr std::int64_t kRowFusedMinWidth = 2;     // rows below 1024 elements take one warp, as in mc_row_reduce
-inline constexpr std::int64_t kRowFusedMaxWidth = 16384;  // at most 32 registers per full-shaped value and thread
+inline constexpr std::int64_t kRowFusedMaxWidth = 32768;  // at most 32 registers per full-shaped value and thread
 
 struct RowOperand {
     enum class Kind { Full, PerRow, RowVector, Scalar };

@@ -483,7 +483,7 @@ def test_constant_row_reductions_fold_to_known_answers(mc):
 
 
 def test_row_reduction_lowering_absorbs_and_rematerializes_producers(mc):
-    separate = {"fuse_rows": 0}  # the per-step form; rows of up to 16384 elements otherwise become one kernel
+    separate = {"fuse_rows": 0}  # the per-step form; rows of up to 32768 elements otherwise become one kernel
     g = mc.HostGraph(mc.graph_path("x2_layernorm"), dims="M=64,N=4096")
     plain = g.launch_plan({"rematerialize": 0, **separate})
     assert "row_sum total rows of 4096 prologue_ops=0" in plain
@@ -523,7 +523,10 @@ def test_runs_of_row_steps_become_one_kernel(mc):
     wide = mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=16384")
     assert "row_fused" in wide.launch_plan({}) and "__launch_bounds__(512)" in wide.plan_sources({})
     assert "__launch_bounds__(512)" in wide.plan_sources({"fuse_rows": 0})  # the separate reduction shares the row's thread count
-    assert "row_fused" not in mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=20000").launch_plan({})
+    widest = mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=32768")
+    assert "row_fused" in widest.launch_plan({}) and "__launch_bounds__(1024)" in widest.plan_sources({})
+    assert "1024 threads per row, 32 element(s) per thread" in widest.plan_sources({})
+    assert "row_fused" not in mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=40000").launch_plan({})
     # values that something outside the run reads are written; a matmul ends a run
     text = ("input x : f32[64, 2048]\nconst w : f32[2048, 64] = uniform(seed=3, lo=-1, hi=1)\nm = row_max x\nd = sub x, m\n"
             "e = exp d\ns = row_sum e\ny = div e, s\nz = matmul y, w\noutput z, s")
