@@ -100,6 +100,9 @@ MCD_API int mcd_jit_occupancy(void* function, int block_threads, size_t dynamic_
 MCD_API int mcd_jit_set_dynamic_smem(void* function, size_t bytes);
 MCD_API int mcd_launch(void* function, unsigned grid_x, unsigned grid_y, unsigned grid_z, unsigned block_x,
                        size_t dynamic_smem, void* stream, void** params);
+/* The same with thread-block clusters of `cluster_x` CTAs along x (grid_x a multiple of it). */
+MCD_API int mcd_launch_cluster(void* function, unsigned grid_x, unsigned cluster_x, unsigned block_x, size_t dynamic_smem,
+                               void* stream, void** params);
 /* Launch-list replay (the reference names CUDA-graph replay of enqueue as its next step, README.md:554-556).
  * Between begin and end every launch issued on `stream` through this layer is recorded instead of run;
  * end returns an executable graph that mcd_graph_launch replays on any stream of the same device. */
@@ -169,7 +172,10 @@ MCD_API int mcd_transpose_f32(const float* src, float* dst, long long rows, long
  *  c, c16      outputs: float [m,n] with leading dimension ldc (may be NULL) and/or a 16-bit copy
  *              of kind `c16_kind` with leading dimension ldc16 (may be NULL).
  *  splits      > 1 divides K; partial sums go to `workspace` (splits*m*n floats) and are added in a
- *              fixed order, so results do not depend on scheduling.
+ *              fixed order, so results do not depend on scheduling. With variant bit 64 a tensor-core
+ *              matmul whose effective split count is 2, 4 or 8 adds them inside one launch instead (the K
+ *              slices of a tile form a thread-block cluster and meet in distributed shared memory, same
+ *              order, same bits): it then needs no workspace and mcd_gemm_launches() is 1.
  *  function    NULL: the built-in kernel without epilogue. Otherwise a kernel obtained from
  *              mcd_jit_kernel for the source returned by mcd_gemm_source(arith) with a generated
  *              `mc_epilogue`; `epilogue_inputs` are its extra operands.
@@ -194,7 +200,8 @@ typedef struct mcd_gemm_args {
     const float* epilogue_inputs[MCD_MAX_EPILOGUE_INPUTS];
     int num_epilogue_inputs;
     unsigned int* status; /* device word: a kernel that gives up a bounded wait ORs an error code in */
-    int variant;          /* tuning variant, 0 = default */
+    int variant;          /* tuning variant, 0 = default; bit 64: split tensor-core matmuls add their partial tiles inside
+                             thread-block clusters instead of through the workspace and a second launch */
     int tile_n;           /* tensor-core arithmetic: columns per tile, 0 or 256 = default, 128 or 64 = narrow tiles
                              for small unsplit problems (one-CTA kernel) */
     int has_epilogue;     /* non-zero when the launch carries a generated epilogue; set it before asking for the
@@ -217,6 +224,10 @@ MCD_API size_t mcd_gemm_dynamic_smem(int arith);
  * memory is kept per device): for a sequence of device ordinals, first[i] = 1 where a launch on
  * devices[i] would run the set-up, 0 where it was done by an earlier element. Touches no GPU. */
 MCD_API int mcd_per_device_once_probe(const int* devices, int count, int* first);
+/* How many thread-block clusters of `cluster_size` CTAs of the one-CTA tensor-core kernel the current device can run
+ * at once (cudaOccupancyMaxActiveClusters): a split matmul that reduces inside clusters runs in one wave only when
+ * its tiles do not exceed this. */
+MCD_API int mcd_gemm_max_active_clusters(int arith, int b_transposed, int cluster_size, int* clusters);
 /* Whether tcgen05 kernels can run on `device` (compute capability 10.x). */
 MCD_API int mcd_tensor_core_supported(int device, int arith);
 

@@ -91,6 +91,16 @@ int tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes) {
     return static_cast<int>(std::max<std::int64_t>(splits, 1));
 }
 
+bool tensor_core_cluster_reduce(int k, int elem_bytes, int splits, int tile_n, int gemm_variant) {
+    if ((gemm_variant & 64) == 0 || (tile_n != 0 && tile_n != 256)) return false;
+    const int block_k = 128 / elem_bytes;
+    const int k_blocks = (k + block_k - 1) / block_k;
+    const int asked = std::max(1, std::min(splits, k_blocks));
+    const int per = (k_blocks + asked - 1) / asked;
+    const int effective = (k_blocks + per - 1) / per;
+    return effective == 2 || effective == 4 || effective == 8;
+}
+
 MatmulKernel resolve_matmul_kernel(MatmulKernel kernel, int m, int n, int k, int sm_count) {
     if (kernel != MatmulKernel::Auto) return kernel;
     return split_k_splits(m, n, k, sm_count) > 1 ? MatmulKernel::SplitK : MatmulKernel::DoubleBuffered;
@@ -443,6 +453,10 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
         // yield correct products on B200, while the K-major form does. 16-bit operands work in both forms.
         s.rhs_transposed = is_tensor_core(kernel) && (rhs_transposed || kernel == MatmulKernel::TensorCoreTf32);
         s.launches = s.splits > 1 ? 2 : 1;
+        if (is_tensor_core(kernel) && s.splits > 1 &&
+            tensor_core_cluster_reduce(s.k, kernel == MatmulKernel::TensorCoreTf32 ? 4 : 2, s.splits, s.tile_n, options.gemm_variant)) {
+            s.launches = 1;  // the K slices of a tile meet inside a thread-block cluster: no second launch, no workspace
+        }
         return s;
     };
 
@@ -582,7 +596,7 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
     for (std::size_t i = 0; i < out.steps.size(); ++i) {
         const Step& s = out.steps[i];
         out.kernel_launches += static_cast<std::size_t>(s.launches) + out.after_step[i].size();
-        if (s.kind == Step::Kind::Matmul && s.splits > 1) {
+        if (s.kind == Step::Kind::Matmul && s.splits > 1 && s.launches > 1) {
             out.workspace_bytes = std::max(out.workspace_bytes, static_cast<std::size_t>(s.splits) * s.m * s.n * sizeof(float));
         }
     }

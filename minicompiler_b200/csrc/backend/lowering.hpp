@@ -52,6 +52,11 @@ int tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes);
 // the SMs with 128 x 256 tiles nor are worth a K split (operand traffic of the narrow tiling at most this many bytes).
 constexpr std::int64_t kNarrowTileTrafficLimit = 128LL << 20;
 int tensor_core_tile_n(int m, int n, int k, int sm_count, int elem_bytes);
+// Whether a tensor-core matmul split `splits` ways adds its partial tiles inside thread-block clusters (one launch,
+// no workspace): asked for with gemm_variant bit 64, for 2, 4 or 8 effective K splits of 256-column tiles (off by
+// default: it measured no faster than the second launch it saves). The device layer
+// applies the same rule when it launches (tc_cluster_reduce in gemm_launch.cu; a host test compares the two).
+bool tensor_core_cluster_reduce(int k, int elem_bytes, int splits, int tile_n, int gemm_variant);
 MatmulKernel resolve_matmul_kernel(MatmulKernel kernel, int m, int n, int k, int sm_count);
 int matmul_splits(MatmulKernel kernel, int m, int n, int k, int sm_count);
 std::size_t matmul_workspace_bytes(MatmulKernel kernel, int m, int n, int splits);

@@ -76,6 +76,7 @@ const DriverApi* driver_api() {
         ok = resolve("cuModuleGetFunction", api.ModuleGetFunction) && ok;
         ok = resolve("cuModuleUnload", api.ModuleUnload) && ok;
         ok = resolve("cuLaunchKernel", api.LaunchKernel) && ok;
+        ok = resolve("cuLaunchKernelEx", api.LaunchKernelEx) && ok;
         ok = resolve("cuFuncSetAttribute", api.FuncSetAttribute) && ok;
         ok = resolve("cuOccupancyMaxActiveBlocksPerMultiprocessor", api.OccupancyMaxActiveBlocksPerMultiprocessor) && ok;
         ok = resolve("cuTensorMapEncodeTiled", api.TensorMapEncodeTiled) && ok;
@@ -543,6 +544,32 @@ int mcd_launch(void* function, unsigned grid_x, unsigned grid_y, unsigned grid_z
     return check_drv(drv->LaunchKernel(static_cast<CUfunction>(function), grid_x, grid_y, grid_z, block_x, 1, 1,
                                        static_cast<unsigned>(dynamic_smem), static_cast<CUstream>(stream), params, nullptr),
                      "cuLaunchKernel");
+}
+
+int mcd_launch_cluster(void* function, unsigned grid_x, unsigned cluster_x, unsigned block_x, size_t dynamic_smem, void* stream,
+                       void** params) {
+    const DriverApi* drv = driver_api();
+    if (drv == nullptr) return fail("the CUDA driver API is unavailable");
+    if (cluster_x == 0 || grid_x % cluster_x != 0) return fail("mcd_launch_cluster: the grid is not a whole number of clusters");
+    CUlaunchAttribute attribute;
+    attribute.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+    attribute.value.clusterDim.x = cluster_x;
+    attribute.value.clusterDim.y = 1;
+    attribute.value.clusterDim.z = 1;
+    CUlaunchConfig config;
+    std::memset(&config, 0, sizeof config);
+    config.gridDimX = grid_x;
+    config.gridDimY = 1;
+    config.gridDimZ = 1;
+    config.blockDimX = block_x;
+    config.blockDimY = 1;
+    config.blockDimZ = 1;
+    config.sharedMemBytes = static_cast<unsigned>(dynamic_smem);
+    config.hStream = static_cast<CUstream>(stream);
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return check_drv(drv->LaunchKernelEx(&config, static_cast<CUfunction>(function), params, nullptr), "cuLaunchKernelEx");
 }
 
 // ------------------------------------------------------------ graph replay

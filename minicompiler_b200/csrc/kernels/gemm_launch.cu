@@ -308,6 +308,19 @@ int tc_splits(const mcd_gemm_args* a) {
     return (k_blocks + per - 1) / per;
 }
 
+// Whether a split tensor-core launch adds its partial tiles inside thread-block clusters (one launch, no workspace):
+// asked for with variant bit 64, for 2, 4 or 8 effective K splits of 256-column tiles. Off by default: measured on
+// B200 it is no faster than the workspace and the second launch it saves (16 x 8192 x 8192 split 4 ways: 40.4 against
+// 39.9 us; 128 x 8192 x 8192: 51.2 against 46.1 us; 1024 x 1024 x 65536: 122.9 against 117.8 us) - the two hand-shakes
+// between the CTAs of a cluster cost about 3 us and the exchange through distributed shared memory the rest. The
+// lowering mirrors this rule (tensor_core_cluster_reduce in lowering.cpp) to count launches and size the workspace.
+bool tc_cluster_reduce(const mcd_gemm_args* a) {
+    if (a->arith == MCD_GEMM_F32 || (a->variant & 64) == 0) return false;
+    if (a->tile_n != 0 && a->tile_n != MC_TC_BN) return false;
+    const int splits = tc_splits(a);
+    return splits == 2 || splits == 4 || splits == 8;
+}
+
 // Whether the launch goes to the SM-pair kernel: unsplit problems with at least half a wave of 256 x 256 pair
 // tiles (2048^3: 64 tiles on 74 pairs, 739 against 653 TFLOP/s); variant bit 8 forces it for any unsplit problem,
 // bit 4 turns it off.
@@ -355,7 +368,8 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     int splits = std::max(1, std::min(a->splits, k_blocks));
     const int per = (k_blocks + splits - 1) / splits;
     splits = (k_blocks + per - 1) / per;
-    if (splits > 1 && a->workspace == nullptr) return fail("mcd_gemm: a split matmul needs a workspace");
+    const bool cluster = tc_cluster_reduce(a);
+    if (splits > 1 && !cluster && a->workspace == nullptr) return fail("mcd_gemm: a split matmul needs a workspace");
 
     CUtensorMapDataType type = tf32 ? ((a->variant & 1) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_TFLOAT32)
                                : a->arith == MCD_GEMM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -395,6 +409,7 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     p.k_blocks_per_split = per;
     p.splits = splits;
     p.wide = 0;
+    p.cluster_reduce = cluster ? splits : 0;
     p.staged = (a->variant & 128) == 0 ? 1 : 0;
     // Tiles that do not fill the last wave of CTAs are cut in two when both halves of all of them fit in one wave.
     const int sms = sm_count_of_current_device();
@@ -441,6 +456,12 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     const int tiles = (all_tiles + p.half_tiles) * splits;
     const unsigned grid = static_cast<unsigned>(std::max(1, std::min(tiles, sms)));
 
+    if (a->function != nullptr && cluster) {
+        // One CTA per (tile, K slice); the slices of a tile are consecutive block indices, hence one cluster.
+        void* params[] = {&map_a, &map_b, &p, &epi};
+        return mcd_launch_cluster(a->function, static_cast<unsigned>(tiles), static_cast<unsigned>(splits), MC_TC_THREADS,
+                                  MC_TC_SMEM_BYTES, s, params);
+    }
     if (a->function != nullptr && splits == 1) {
         void* params[] = {&map_a, &map_b, &p, &epi};
         return mcd_launch(a->function, grid, 1, 1, MC_TC_THREADS, MC_TC_SMEM_BYTES, s, params);
@@ -458,6 +479,22 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
                 return rc;
             }
         }
+    }
+    if (cluster) {
+        cudaLaunchAttribute attribute;
+        attribute.id = cudaLaunchAttributeClusterDimension;
+        attribute.val.clusterDim.x = static_cast<unsigned>(splits);
+        attribute.val.clusterDim.y = 1;
+        attribute.val.clusterDim.z = 1;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(static_cast<unsigned>(tiles), 1, 1);
+        config.blockDim = dim3(MC_TC_THREADS, 1, 1);
+        config.dynamicSmemBytes = MC_TC_SMEM_BYTES;
+        config.stream = s;
+        config.attrs = &attribute;
+        config.numAttrs = 1;
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return check_rt(cudaLaunchKernelEx(&config, kernel, map_a, map_b, p, epi), "cudaLaunchKernelEx(mc_gemm_tc, cluster)");
     }
     kernel<<<grid, MC_TC_THREADS, MC_TC_SMEM_BYTES, s>>>(map_a, map_b, p, epi);
     if (int rc = launched("mc_gemm_tc")) return rc;
@@ -491,12 +528,8 @@ extern "C" int mcd_gemm_launches(const mcd_gemm_args* a) {
         splits = (a->k + k_per_split - 1) / k_per_split;
         return splits > 1 ? 2 : 1;
     }
-    const int block_k = a->arith == MCD_GEMM_TF32 ? 32 : 64;
-    const int k_blocks = (a->k + block_k - 1) / block_k;
-    int splits = std::max(1, std::min(a->splits, k_blocks));
-    const int per = (k_blocks + splits - 1) / splits;
-    splits = (k_blocks + per - 1) / per;
-    return splits > 1 ? 2 : 1;
+    if (tc_cluster_reduce(a)) return 1;
+    return tc_splits(a) > 1 ? 2 : 1;
 }
 
 extern "C" const char* mcd_gemm_source(int arith) {
@@ -531,6 +564,28 @@ extern "C" size_t mcd_gemm_dynamic_smem(int arith) {
     static_assert(MC_TC2_SMEM_BYTES >= MC_TC_SMEM_BYTES, "the pair kernels set the limit of both tensor-core families");
     static_assert(MC_TC2_SMEM_BYTES + 64 <= 227 * 1024, "dynamic plus static shared memory of the pair kernel");
     return (arith == MCD_GEMM_TF32 || arith == MCD_GEMM_BF16 || arith == MCD_GEMM_F16) ? MC_TC2_SMEM_BYTES : 0;
+}
+
+extern "C" int mcd_gemm_max_active_clusters(int arith, int b_transposed, int cluster_size, int* clusters) {
+    using Kernel = void (*)(const McTensorMap, const McTensorMap, const McTcParams, const McEpilogueArgs);
+    const bool tf32 = arith == MCD_GEMM_TF32;
+    Kernel kernel = tf32 ? (b_transposed ? mc_gemm_tc_tf32_bk : mc_gemm_tc_tf32_bmn) : (b_transposed ? mc_gemm_tc_h16_bk : mc_gemm_tc_h16_bmn);
+    if (int rc = check_rt(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_TC_SMEM_BYTES),
+                          "cudaFuncSetAttribute(max dynamic shared memory)")) {
+        return rc;
+    }
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = static_cast<unsigned>(cluster_size);
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(cluster_size) * 64, 1, 1);
+    config.blockDim = dim3(MC_TC_THREADS, 1, 1);
+    config.dynamicSmemBytes = MC_TC_SMEM_BYTES;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    return check_rt(cudaOccupancyMaxActiveClusters(clusters, kernel, &config), "cudaOccupancyMaxActiveClusters");
 }
 
 extern "C" int mcd_per_device_once_probe(const int* devices, int count, int* first) {

@@ -20,6 +20,13 @@
 // B is read either as stored by the graph ([k,n] row-major: "MN-major" operand,
 // mc_gemm_tc_*_bmn) or from a [n,k] copy ("K-major", mc_gemm_tc_*_bk).
 //
+// Split K without a workspace (p.cluster_reduce = S in {2, 4, 8}): the S work items of a tile form a thread-block
+// cluster, one K slice each. When every CTA of the cluster has finished its MMAs, each sends the S-th part of its
+// partial tile that a peer owns into that peer's shared memory (distributed shared memory, st.shared::cluster,
+// in the space the operand ring no longer needs); every CTA then adds the S partial sums of its columns in slice
+// order, applies the epilogue and stores them. The partial sums never touch global memory, there is no second
+// launch, and the order of the additions is that of the separate reduction kernel (bit-identical results).
+//
 // Every wait is bounded: a wait that exceeds MC_TC_WAIT_NS of wall time records
 // MC_TC_ERR_* in *status, raises a CTA-wide abort flag and every role leaves its
 // loop; the CTA then waits (bounded) for its TMA copies in flight, frees its
@@ -41,6 +48,7 @@
 #define MC_TC_ERR_MMA 0x2u
 #define MC_TC_ERR_EPILOGUE 0x4u
 #define MC_TC_ERR_DRAIN 0x8u
+#define MC_TC_ERR_CLUSTER 0x10u
 
 struct __align__(64) McTensorMap {
     unsigned long long opaque[16];
@@ -63,6 +71,8 @@ struct McTcParams {
     int staged;      // SM-pair kernel only: outputs leave through shared memory as whole row segments
     int tile_n;      // one-CTA kernel only: columns per tile, 256 (default), 128 or 64; narrow tiles let a small
                      // problem fill the SMs in one launch instead of splitting K (idesc carries the same N)
+    int cluster_reduce;  // one-CTA kernel only: 0, or the K splits of a tile are the CTAs of a cluster of this size,
+                         // which add their partial tiles through distributed shared memory (one work item per CTA)
 };
 
 __device__ __forceinline__ unsigned mc_smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -116,6 +126,81 @@ __device__ __forceinline__ bool mc_mbar_wait(unsigned bar, unsigned parity, vola
         }
     }
     return true;
+}
+
+
+__device__ __forceinline__ unsigned mc_cluster_ctarank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// The shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ unsigned mc_mapa(unsigned addr, unsigned rank) {
+    unsigned out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+    return out;
+}
+
+__device__ __forceinline__ void mc_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void mc_mbar_arrive_cluster(unsigned cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// Arrive with release semantics at cluster scope: shared-memory writes to the barrier's CTA made before it (by
+// threads ordered before the arriving one) are visible to a waiter that acquires at cluster scope.
+__device__ __forceinline__ void mc_mbar_arrive_release_cluster(unsigned cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// A non-blocking test: try_wait may put the thread to sleep until the phase completes or a system-chosen time limit
+// passes, and an arrival from another CTA of the cluster did not end that sleep early (each such wait then cost
+// several microseconds); the waits on cluster barriers therefore poll.
+__device__ __forceinline__ bool mc_mbar_try_wait_cluster(unsigned bar, unsigned parity) {
+    unsigned done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// mc_mbar_wait for a barrier that CTAs of the cluster arrive on.
+__device__ __forceinline__ bool mc_mbar_wait_cluster(unsigned bar, unsigned parity, volatile int* abort_flag, unsigned* status,
+                                                     unsigned err_code) {
+    if (mc_mbar_try_wait_cluster(bar, parity)) return true;
+    const unsigned long long t0 = mc_globaltimer();
+    unsigned spins = 0;
+    while (!mc_mbar_try_wait_cluster(bar, parity)) {
+        if ((++spins & 255u) == 0u) {
+            if (*abort_flag != 0) return false;
+            if (mc_globaltimer() - t0 > MC_TC_WAIT_NS) {
+                if (status != nullptr) atomicOr(status, err_code);
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void mc_st_cluster_v4(unsigned cluster_addr, unsigned a, unsigned b, unsigned c, unsigned d) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+__device__ __forceinline__ float mc_ld_shared_f32(unsigned addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
 }
 
 __device__ __forceinline__ void mc_tma_load_2d(unsigned smem_dst, const McTensorMap* map, unsigned bar, int c0, int c1) {
@@ -216,6 +301,10 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
     const unsigned bar_empty = bars_base + 8 * MC_TC_STAGES;
     const unsigned bar_tmem_full = bars_base + 16 * MC_TC_STAGES;
     const unsigned bar_tmem_empty = bar_tmem_full + 16;
+    // cluster reduction: peers_done (every CTA of the cluster has finished its MMAs), data_ready (every epilogue warp
+    // of every CTA has delivered its partial sums)
+    const unsigned bar_peers_done = bar_tmem_empty + 16;
+    const unsigned bar_data_ready = bar_peers_done + 8;
     __shared__ unsigned tmem_base_slot;
     __shared__ int abort_flag_storage;
     volatile int* abort_flag = &abort_flag_storage;
@@ -239,6 +328,10 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
             mc_mbar_init(bar_tmem_full + 8 * a, 1);
             mc_mbar_init(bar_tmem_empty + 8 * a, MC_TC_EPILOGUE_WARPS);  // one arrival per epilogue warp
         }
+        if (p.cluster_reduce > 1) {
+            mc_mbar_init(bar_peers_done, (unsigned)p.cluster_reduce);
+            mc_mbar_init(bar_data_ready, (unsigned)(p.cluster_reduce * MC_TC_EPILOGUE_WARPS));
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -251,6 +344,7 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = tmem_base_slot;
+    if (p.cluster_reduce > 1) mc_cluster_sync();  // every CTA's barriers exist before a peer arrives on them
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -373,6 +467,86 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
         unsigned acc_phase = 0;
         bool ok = true;
         const bool partial = p.splits > 1;
+        if (p.cluster_reduce > 1) {
+            // ---- K slices of one tile as a cluster: partial tiles meet in distributed shared memory
+            const int S = p.cluster_reduce;
+            const unsigned my_rank = mc_cluster_ctarank();
+            int mb, nb, split, half;
+            mc_tc_decode((int)blockIdx.x, tiles_m, tiles_n, p.splits, 0, mb, nb, split, half);
+            const int cw = bn / S;        // columns of the tile each CTA finishes
+            const int pitch = cw + 4;     // floats per row of a received slot (the pad spreads rows over the banks)
+            const unsigned recv_base = tiles_base;  // slot r (from rank r): [128 rows][pitch] floats, in the operand ring's space
+            ok = mc_mbar_wait(bar_tmem_full, 0u, abort_flag, p.status, MC_TC_ERR_EPILOGUE);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // This CTA's MMAs are complete, so its ring is free: tell every CTA of the cluster, then wait for all.
+                if (warp == 2 && lane == 0) {
+                    for (int r = 0; r < S; ++r) mc_mbar_arrive_release_cluster(mc_mapa(bar_peers_done, (unsigned)r));
+                }
+                ok = mc_mbar_wait_cluster(bar_peers_done, 0u, abort_flag, p.status, MC_TC_ERR_CLUSTER);
+                ok = __all_sync(0xffffffffu, ok);
+            }
+            if (ok) {
+                const int row_in_tile = quarter * 32 + lane;
+                const bool row_valid = mb * MC_TC_BM + row_in_tile < p.m;
+                for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {
+                    const int col = col_begin + chunk * 32;  // within the tile
+                    if (nb * bn + col >= p.n) break;         // warp-uniform: nobody reads these columns
+                    unsigned v[32];
+                    mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)col, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (row_valid) {
+                        const int owner = col / cw;
+                        const unsigned local = recv_base + (unsigned)((((int)my_rank * MC_TC_BM + row_in_tile) * pitch + col % cw) * 4);
+                        const unsigned remote = mc_mapa(local, (unsigned)owner);
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) mc_st_cluster_v4(remote + 4u * j, v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    }
+                }
+                asm volatile("fence.acq_rel.cluster;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    for (int r = 0; r < S; ++r) mc_mbar_arrive_release_cluster(mc_mapa(bar_data_ready, (unsigned)r));
+                }
+                ok = mc_mbar_wait_cluster(bar_data_ready, 0u, abort_flag, p.status, MC_TC_ERR_CLUSTER);
+                ok = __all_sync(0xffffffffu, ok);
+            }
+            if (ok) {
+                // Columns [my_rank * cw, +cw) of the tile. Rows go round the 8 warps (so a problem of 16 rows still uses
+                // all of them), lanes along the columns; a row's S x cw/32 values are requested together, then the
+                // slices are added in index order.
+                const float* recv = static_cast<const float*>(__cvta_shared_to_generic(recv_base));
+                const int rows_here = min(MC_TC_BM, p.m - mb * MC_TC_BM);
+                const int per_lane = cw / 32;  // 1, 2 or 4 columns per lane
+                for (int r = warp - 2; r < rows_here; r += MC_TC_EPILOGUE_WARPS) {
+                    const int row = mb * MC_TC_BM + r;
+                    float part[8][4];
+#pragma unroll
+                    for (int z = 0; z < 8; ++z) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            part[z][j] = (z < S && j < per_lane) ? recv[(z * MC_TC_BM + r) * pitch + lane + 32 * j] : 0.0f;
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (j >= per_lane) break;
+                        const int colg = nb * bn + (int)my_rank * cw + lane + 32 * j;
+                        if (colg >= p.n) continue;
+                        float sum = part[0][j];
+#pragma unroll
+                        for (int z = 1; z < 8; ++z) {
+                            if (z < S) sum += part[z][j];
+                        }
+                        sum = mc_epilogue(sum, (unsigned)row, (unsigned)colg, epi);
+                        if (p.c != nullptr) p.c[(long long)row * p.ldc + colg] = sum;
+                        if (p.c16 != nullptr) p.c16[(long long)row * p.ldc16 + colg] = mc_to_half(sum, p.c16_kind);
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        } else
         for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
             int mb, nb, split, half;
             mc_tc_decode(item, tiles_m, tiles_n, p.splits, p.half_tiles, mb, nb, split, half);
@@ -457,6 +631,8 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
     __syncwarp();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    // No CTA of a cluster lets go of its shared memory while a peer may still write to it or arrive on its barriers.
+    if (p.cluster_reduce > 1) mc_cluster_sync();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");

@@ -25,28 +25,6 @@
 #define MC_TC2_STAGING_PER_WARP 4096
 #define MC_TC2_SMEM_BYTES (MC_TC2_STAGES * MC_TC2_STAGE_BYTES + 1024 + 256 + MC_TC_EPILOGUE_WARPS * MC_TC2_STAGING_PER_WARP)
 
-__device__ __forceinline__ unsigned mc_cluster_ctarank() {
-    unsigned r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-
-// The shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
-__device__ __forceinline__ unsigned mc_mapa(unsigned addr, unsigned rank) {
-    unsigned out;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
-    return out;
-}
-
-__device__ __forceinline__ void mc_cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void mc_mbar_arrive_cluster(unsigned cluster_addr) {
-    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-
 // TMA load whose completion is counted on a barrier that may sit in the peer CTA of the pair.
 __device__ __forceinline__ void mc_tma_load_2d_pair(unsigned smem_dst, const McTensorMap* map, unsigned bar_cluster_addr, int c0,
                                                     int c1) {

@@ -304,6 +304,29 @@ def test_tensor_core_kernel_direct(mc, oracle, name, arith, half, u, sub, layout
 
 @pytest.mark.parametrize("layout", [False, True])
 @pytest.mark.parametrize("name,arith,half,u,sub", TC_KINDS)
+def test_tensor_core_cluster_reduction_direct(mc, oracle, name, arith, half, u, sub, layout):
+    """K split 2, 4 or 8 ways with the partial tiles added inside thread-block clusters (through distributed shared
+    memory, one launch; variant bit 64) gives the bits of the default workspace-and-second-launch form: both add the
+    slices in index order. C is pre-filled with NaN; ragged M, N and K, a single row block, several tiles."""
+    if half is None and not layout:
+        pytest.skip("TF32 reads B as a [n,k] copy only")
+    for m, k, n in [(128, 512, 256), (16, 2048, 512), (300, 1004, 36), (33, 264, 72), (130, 4096, 1000), (256, 8192, 768)]:
+        if half is None and (k % 4 or n % 4):
+            continue
+        a = oracle.uniform_values(m * k, 1, -1, 1).reshape(m, k)
+        b = oracle.uniform_values(k * n, 2, -1, 1).reshape(k, n)
+        exact, abs_dot = exact_and_abs(a, b)
+        for splits in [2, 4, 8]:
+            if (k + (31 if half is None else 63)) // (32 if half is None else 64) < splits:
+                continue
+            in_cluster = _device_gemm(mc, arith, a, b, splits, b_transposed=layout, half=half, variant=64)
+            through_workspace = _device_gemm(mc, arith, a, b, splits, b_transposed=layout, half=half)
+            assert np.array_equal(in_cluster, through_workspace), f"{name} {m}x{k}x{n} splits={splits} transposed={layout}"
+            check_bound(in_cluster, exact, abs_dot, k, u, sub, f"{name} {m}x{k}x{n} splits={splits} transposed={layout}")
+
+
+@pytest.mark.parametrize("layout", [False, True])
+@pytest.mark.parametrize("name,arith,half,u,sub", TC_KINDS)
 def test_tensor_core_narrow_tiles_direct(mc, oracle, name, arith, half, u, sub, layout):
     """128 x 128 and 128 x 64 tiles of the one-CTA kernel give the bits of its 128 x 256 tiles."""
     if half is None and not layout:

@@ -631,3 +631,42 @@ def test_row_slicing_analysis(mc):
     sliced = mc.HostGraph(mc.graph_path("c3_ffn"), dims={"T": 512, "D": 128, "H": 256}).row_slicing(128)
     assert "x = input : f32[128,128]" in sliced and "w1 = const <32768 values> : f32[128,256]" in sliced
     assert "y = fused %7, %4, %0 : f32[128,128]  (output)" in sliced
+
+
+def test_split_tensor_core_matmuls_that_reduce_in_a_cluster_need_one_launch_and_no_workspace(mc):
+    """With gemm_variant bit 64 a tensor-core matmul whose K is split 2, 4 or 8 ways adds its partial tiles inside
+    thread-block clusters: one launch, no workspace. The lowering (which counts launches and sizes the workspace) and the device layer (which
+    launches) each apply the rule; they must agree for every shape and split count."""
+    lib = mc.lib()
+
+    class GemmArgs(ctypes.Structure):
+        _fields_ = [("arith", ctypes.c_int), ("m", ctypes.c_int), ("n", ctypes.c_int), ("k", ctypes.c_int), ("a", ctypes.c_void_p),
+                    ("b", ctypes.c_void_p), ("lda", ctypes.c_longlong), ("ldb", ctypes.c_longlong), ("b_transposed", ctypes.c_int),
+                    ("c", ctypes.c_void_p), ("ldc", ctypes.c_longlong), ("c16", ctypes.c_void_p), ("c16_kind", ctypes.c_int),
+                    ("ldc16", ctypes.c_longlong), ("splits", ctypes.c_int), ("workspace", ctypes.c_void_p),
+                    ("function", ctypes.c_void_p), ("reduce_function", ctypes.c_void_p), ("epilogue_inputs", ctypes.c_void_p * 6),
+                    ("num_epilogue_inputs", ctypes.c_int), ("status", ctypes.c_void_p), ("variant", ctypes.c_int),
+                    ("tile_n", ctypes.c_int), ("has_epilogue", ctypes.c_int)]
+
+    lib.mcd_gemm_launches.restype = ctypes.c_int
+    text = "dim M = 8\ndim N = 8\ndim K = 8\ninput a : f32[M, K]\ninput b : f32[K, N]\nc = matmul a, b\noutput c"
+    for m, n, k in [(128, 8192, 8192), (16, 8192, 8192), (1024, 1024, 65536), (256, 2048, 512), (128, 256, 100000), (384, 1024, 4096),
+                    (640, 1280, 2048), (128, 4096, 520), (4096, 4096, 4096)]:
+        for name, arith, elem in (("tensor_core_bf16", 2, 2), ("tensor_core_tf32", 1, 4)):
+            for variant in (0, 64):
+                plan = mc.HostGraph(text=text, dims={"M": m, "N": n, "K": k}).launch_plan({"matmul": name, "gemm_variant": variant})
+                splits = int(re.search(r"splits=(\d+)", plan).group(1))
+                launches = int(re.search(r"launches=(\d+)\n", plan).group(1))
+                workspace = int(re.search(r"workspace_bytes=(\d+)", plan).group(1))
+                tile_n = int(m_.group(1)) if (m_ := re.search(r"tile_n=(\d+)", plan)) else 0
+                args = GemmArgs(arith=arith, m=m, n=n, k=k, splits=splits, variant=variant, tile_n=tile_n)
+                assert lib.mcd_gemm_launches(ctypes.byref(args)) == launches, (m, n, k, name, variant, plan)
+                assert (workspace > 0) == (launches == 2), plan
+                if variant == 0:
+                    assert launches == (2 if splits > 1 else 1)
+    # the config shapes: skinny and tall-K problems split 4 ways; one launch each when the clusters are asked for
+    for m, n, k in [(128, 8192, 8192), (16, 8192, 8192), (1024, 1024, 65536)]:
+        plan = mc.HostGraph(text=text, dims={"M": m, "N": n, "K": k}).launch_plan({"matmul": "tensor_core_bf16", "gemm_variant": 64})
+        assert "splits=4" in plan and "launches=1\n" in plan and "workspace_bytes=0" in plan, plan
+        plan = mc.HostGraph(text=text, dims={"M": m, "N": n, "K": k}).launch_plan({"matmul": "tensor_core_bf16"})
+        assert "splits=4" in plan and "launches=2\n" in plan
