@@ -510,7 +510,7 @@ private:
         MCD_TRY(mcd_stream_synchronize(stream_));
         if (word != 0) {
             MCD_TRY(mcd_memset(status_word(), 0, sizeof word, stream_));
-            return Error{"a tensor-core matmul gave up a bounded wait (status 0x" + to_hex(word) +
+            return Error{"a matmul kernel gave up a bounded wait (status 0x" + to_hex(word) +
                          "): results of this run are incomplete"};
         }
         return Status();
@@ -979,10 +979,9 @@ private:
         g.tile_n = step.tile_n;
         g.workspace = step.splits > 1 ? workspace : nullptr;
         g.variant = options_.gemm_variant;
-        if (is_tensor_core(step.kernel)) {
-            g.status = status_word();
-            uses_status_ = true;
-        }
+        // Kernels fed by TMA wait on mbarriers; a wait that gives up reports through this word.
+        g.status = status_word();
+        uses_status_ = true;
         if (step.has_epilogue) {
             g.has_epilogue = 1;
             int slot = 0;

@@ -22,6 +22,7 @@
 #include <tuple>
 
 #include "kernels/epilogue.cuh"
+#include "kernels/async_copy.cuh"
 #include "kernels/gemm_f32_simt.cuh"
 #include "kernels/gemm_tcgen05.cuh"
 #include "kernels/gemm_tcgen05_2cta.cuh"
@@ -30,6 +31,7 @@
 namespace mcd {
 extern std::atomic<unsigned long long> g_launches;
 extern const char* const kSourceEpilogue;
+extern const char* const kSourceAsyncCopy;
 extern const char* const kSourceGemmF32;
 extern const char* const kSourceGemmTc;
 extern const char* const kSourceGemmTc2;
@@ -205,39 +207,6 @@ int reduce_splits(const mcd_gemm_args* a, int splits, cudaStream_t s) {
     return launched("mc_splitk_reduce");
 }
 
-int gemm_f32(const mcd_gemm_args* a, cudaStream_t s) {
-    if (a->b_transposed) return fail("mcd_gemm: the FP32 kernel reads B as [k,n]");
-    const int kstep = MC_F32_BK;
-    int splits = std::max(1, a->splits);
-    int k_per_split = ((a->k + splits - 1) / splits + kstep - 1) / kstep * kstep;
-    splits = (a->k + k_per_split - 1) / k_per_split;
-    if (splits > 1 && a->workspace == nullptr) return fail("mcd_gemm: a split matmul needs a workspace");
-    const bool vec = aligned16(a->a) && aligned16(a->b) && (a->c == nullptr || aligned16(a->c)) && a->lda % 4 == 0 &&
-                     a->ldb % 4 == 0 && (splits == 1 || aligned16(a->workspace));
-    const dim3 grid((a->n + MC_F32_BN - 1) / MC_F32_BN, (a->m + MC_F32_BM - 1) / MC_F32_BM, splits);
-    McEpilogueArgs epi = epilogue_args(a);
-    const auto* pa = static_cast<const float*>(a->a);
-    const auto* pb = static_cast<const float*>(a->b);
-    float* pc = a->c;
-    auto* pc16 = static_cast<unsigned short*>(a->c16);
-    int kind = a->c16_kind, m = a->m, n = a->n, k = a->k;
-    long long lda = a->lda, ldb = a->ldb, ldc = a->ldc, ldc16 = a->ldc16;
-    float* ws = a->workspace;
-    if (a->function != nullptr && splits == 1) {
-        // `function` is the entry point mcd_gemm_entry_point named for these arguments.
-        void* params[] = {&pa, &pb, &pc, &pc16, &kind, &m, &n, &k, &lda, &ldb, &ldc, &ldc16, &k_per_split, &ws, &epi};
-        return mcd_launch(a->function, grid.x, grid.y, grid.z, 256, 0, s, params);
-    }
-    if (vec) {
-        mc_gemm_f32_vec<<<grid, 256, 0, s>>>(pa, pb, pc, pc16, kind, m, n, k, lda, ldb, ldc, ldc16, k_per_split, ws, epi);
-    } else {
-        mc_gemm_f32_any<<<grid, 256, 0, s>>>(pa, pb, pc, pc16, kind, m, n, k, lda, ldb, ldc, ldc16, k_per_split, ws, epi);
-    }
-    if (int rc = launched("mc_gemm_f32")) return rc;
-    if (splits > 1) return reduce_splits(a, splits, s);
-    return 0;
-}
-
 unsigned instruction_descriptor(int arith, bool b_is_k_major) {
     // c_format F32 (1) at bit 4; a/b formats at bits 7 and 10 (F16 0, BF16 1, TF32 2);
     // b_major at bit 16 (1 = MN-major); N >> 3 at bit 17; M >> 4 at bit 24.
@@ -259,10 +228,10 @@ struct MapKey {
     const void* base;
     unsigned long long inner, outer, pitch;
     unsigned box_inner, box_outer;
-    int type, elem_bytes;
+    int type, elem_bytes, swizzle;
     bool operator<(const MapKey& o) const {
-        return std::tie(base, inner, outer, pitch, box_inner, box_outer, type, elem_bytes) <
-               std::tie(o.base, o.inner, o.outer, o.pitch, o.box_inner, o.box_outer, o.type, o.elem_bytes);
+        return std::tie(base, inner, outer, pitch, box_inner, box_outer, type, elem_bytes, swizzle) <
+               std::tie(o.base, o.inner, o.outer, o.pitch, o.box_inner, o.box_outer, o.type, o.elem_bytes, o.swizzle);
     }
 };
 std::mutex g_map_mutex;
@@ -270,8 +239,10 @@ std::map<MapKey, CUtensorMap> g_map_cache;
 std::atomic<unsigned long long> g_map_encodes{0};
 
 int encode_map(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, unsigned long long inner,
-               unsigned long long outer, unsigned long long pitch_elems, unsigned box_inner, unsigned box_outer) {
-    const MapKey key{base, inner, outer, pitch_elems, box_inner, box_outer, static_cast<int>(type), elem_bytes};
+               unsigned long long outer, unsigned long long pitch_elems, unsigned box_inner, unsigned box_outer,
+               CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+    const MapKey key{base, inner, outer, pitch_elems, box_inner, box_outer, static_cast<int>(type), elem_bytes,
+                     static_cast<int>(swizzle)};
     {
         std::lock_guard<std::mutex> lock(g_map_mutex);
         const auto hit = g_map_cache.find(key);
@@ -287,7 +258,7 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t elem_strides[2] = {1, 1};
     if (int rc = check_drv(drv->TensorMapEncodeTiled(map, type, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                     CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
                            "cuTensorMapEncodeTiled")) {
         return rc;
@@ -296,6 +267,85 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const
     std::lock_guard<std::mutex> lock(g_map_mutex);
     if (g_map_cache.size() >= 4096) g_map_cache.clear();  // a bound, not a policy: maps are cheap to make again
     g_map_cache.emplace(key, *map);
+    return 0;
+}
+
+int f32_splits(const mcd_gemm_args* a, int* k_per_split) {
+    int splits = std::max(1, a->splits);
+    *k_per_split = ((a->k + splits - 1) / splits + MC_F32_BK - 1) / MC_F32_BK * MC_F32_BK;
+    return (a->k + *k_per_split - 1) / *k_per_split;
+}
+
+// Whether the FP32 launch uses the TMA-fed kernel: operands a tensor map can describe (16-byte aligned bases, row
+// pitches that are multiples of 4 floats), aligned outputs, and at least 512 of K per block - below that the ring's
+// start-up costs more than it saves (256 x 2048 x 512 split 4 ways: 27.2 against 25.7 us; 4096^3: 55.7 against
+// 52.0 TFLOP/s). Variant bit 512 keeps the register-staged kernel, bit 1024 takes the TMA-fed one whatever K is.
+bool f32_uses_tma(const mcd_gemm_args* a) {
+    if ((a->variant & 512) != 0) return false;
+    int k_per_split = 0;
+    const int splits = f32_splits(a, &k_per_split);
+    if (k_per_split < 512 && (a->variant & 1024) == 0) return false;
+    return aligned16(a->a) && aligned16(a->b) && (a->c == nullptr || aligned16(a->c)) && a->lda % 4 == 0 && a->ldb % 4 == 0 &&
+           (splits == 1 || aligned16(a->workspace));
+}
+
+int gemm_f32(const mcd_gemm_args* a, cudaStream_t s) {
+    if (a->b_transposed) return fail("mcd_gemm: the FP32 kernel reads B as [k,n]");
+    int k_per_split = 0;
+    const int splits = f32_splits(a, &k_per_split);
+    if (splits > 1 && a->workspace == nullptr) return fail("mcd_gemm: a split matmul needs a workspace");
+    const bool vec = aligned16(a->a) && aligned16(a->b) && (a->c == nullptr || aligned16(a->c)) && a->lda % 4 == 0 &&
+                     a->ldb % 4 == 0 && (splits == 1 || aligned16(a->workspace));
+    const dim3 grid((a->n + MC_F32_BN - 1) / MC_F32_BN, (a->m + MC_F32_BM - 1) / MC_F32_BM, splits);
+    McEpilogueArgs epi = epilogue_args(a);
+    const auto* pa = static_cast<const float*>(a->a);
+    const auto* pb = static_cast<const float*>(a->b);
+    float* pc = a->c;
+    auto* pc16 = static_cast<unsigned short*>(a->c16);
+    int kind = a->c16_kind, m = a->m, n = a->n, k = a->k;
+    long long lda = a->lda, ldb = a->ldb, ldc = a->ldc, ldc16 = a->ldc16;
+    float* ws = a->workspace;
+    unsigned* status = a->status;
+    if (f32_uses_tma(a)) {
+        McTensorMap map_a, map_b;
+        if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_a), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a->a, a->k, a->m, a->lda,
+                                MC_F32_BK, MC_F32_BM, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+            return rc;
+        }
+        if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_b), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a->b, a->n, a->k, a->ldb,
+                                MC_F32_BN, MC_F32_BK, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+            return rc;
+        }
+        if (a->function != nullptr && splits == 1) {
+            void* params[] = {&map_a, &map_b, &pc, &pc16, &kind, &m, &n, &k, &ldc, &ldc16, &k_per_split, &ws, &status, &epi};
+            return mcd_launch(a->function, grid.x, grid.y, grid.z, 256, MC_F32_TMA_SMEM_BYTES, s, params);
+        }
+        static PerDeviceOnce configured;
+        const int device = current_device();
+        if (configured.first_use(device)) {
+            if (int rc = check_rt(cudaFuncSetAttribute(mc_gemm_f32_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_F32_TMA_SMEM_BYTES),
+                                  "cudaFuncSetAttribute(max dynamic shared memory)")) {
+                configured.forget(device);
+                return rc;
+            }
+        }
+        mc_gemm_f32_tma<<<grid, 256, MC_F32_TMA_SMEM_BYTES, s>>>(map_a, map_b, pc, pc16, kind, m, n, k, ldc, ldc16, k_per_split, ws, status, epi);
+        if (int rc = launched("mc_gemm_f32_tma")) return rc;
+        if (splits > 1) return reduce_splits(a, splits, s);
+        return 0;
+    }
+    if (a->function != nullptr && splits == 1) {
+        // `function` is the entry point mcd_gemm_entry_point named for these arguments.
+        void* params[] = {&pa, &pb, &pc, &pc16, &kind, &m, &n, &k, &lda, &ldb, &ldc, &ldc16, &k_per_split, &ws, &epi};
+        return mcd_launch(a->function, grid.x, grid.y, grid.z, 256, 0, s, params);
+    }
+    if (vec) {
+        mc_gemm_f32_vec<<<grid, 256, 0, s>>>(pa, pb, pc, pc16, kind, m, n, k, lda, ldb, ldc, ldc16, k_per_split, ws, epi);
+    } else {
+        mc_gemm_f32_any<<<grid, 256, 0, s>>>(pa, pb, pc, pc16, kind, m, n, k, lda, ldb, ldc, ldc16, k_per_split, ws, epi);
+    }
+    if (int rc = launched("mc_gemm_f32")) return rc;
+    if (splits > 1) return reduce_splits(a, splits, s);
     return 0;
 }
 
@@ -523,18 +573,16 @@ extern "C" int mcd_gemm(const mcd_gemm_args* args, void* stream) {
 
 extern "C" int mcd_gemm_launches(const mcd_gemm_args* a) {
     if (a->arith == MCD_GEMM_F32) {
-        int splits = std::max(1, a->splits);
-        const int k_per_split = ((a->k + splits - 1) / splits + MC_F32_BK - 1) / MC_F32_BK * MC_F32_BK;
-        splits = (a->k + k_per_split - 1) / k_per_split;
-        return splits > 1 ? 2 : 1;
+        int k_per_split = 0;
+        return f32_splits(a, &k_per_split) > 1 ? 2 : 1;
     }
     if (tc_cluster_reduce(a)) return 1;
     return tc_splits(a) > 1 ? 2 : 1;
 }
 
 extern "C" const char* mcd_gemm_source(int arith) {
-    static const std::string f32 = std::string(kSourceEpilogue) + kSourceGemmF32;
-    static const std::string tc = std::string(kSourceEpilogue) + kSourceGemmTc + kSourceGemmTc2;
+    static const std::string f32 = std::string(kSourceEpilogue) + kSourceAsyncCopy + kSourceGemmF32;
+    static const std::string tc = std::string(kSourceEpilogue) + kSourceAsyncCopy + kSourceGemmTc + kSourceGemmTc2;
     static const std::string reduce = std::string(kSourceEpilogue) + kSourceSplitkReduce;
     if (arith == MCD_GEMM_F32) return f32.c_str();
     if (arith < 0) return reduce.c_str();
@@ -546,6 +594,7 @@ extern "C" const char* mcd_gemm_entry_point(const mcd_gemm_args* a) {
     if (a->arith == MCD_GEMM_F32) {
         const bool vec = aligned16(a->a) && aligned16(a->b) && (a->c == nullptr || aligned16(a->c)) && a->lda % 4 == 0 &&
                          a->ldb % 4 == 0;
+        if (f32_uses_tma(a)) return "mc_gemm_f32_tma";
         return vec ? "mc_gemm_f32_vec" : "mc_gemm_f32_any";
     }
     if (tc_uses_pairs(a)) {
@@ -563,6 +612,7 @@ extern "C" const char* mcd_gemm_entry_point(const mcd_gemm_args* a) {
 extern "C" size_t mcd_gemm_dynamic_smem(int arith) {
     static_assert(MC_TC2_SMEM_BYTES >= MC_TC_SMEM_BYTES, "the pair kernels set the limit of both tensor-core families");
     static_assert(MC_TC2_SMEM_BYTES + 64 <= 227 * 1024, "dynamic plus static shared memory of the pair kernel");
+    if (arith == MCD_GEMM_F32) return MC_F32_TMA_SMEM_BYTES;  // the TMA-fed kernel's ring; harmless for the others
     return (arith == MCD_GEMM_TF32 || arith == MCD_GEMM_BF16 || arith == MCD_GEMM_F16) ? MC_TC2_SMEM_BYTES : 0;
 }
 

@@ -31,6 +31,7 @@
 #define mc_gemm_f32_any mc_na_gemm_f32_any
 #define mc_gemm_f32_body mc_na_gemm_f32_body
 #define mc_splitk_reduce mc_na_splitk_reduce
+#define MC_F32_NO_TMA_KERNEL 1  // this image keeps the register-staged kernels only
 #include "kernels/epilogue.cuh"
 #include "kernels/gemm_f32_simt.cuh"
 #include "kernels/splitk_reduce.cuh"

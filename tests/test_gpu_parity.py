@@ -281,6 +281,23 @@ def test_forced_split_counts_fp32(mc, oracle):
             check_bound(got, exact, abs_dot, k, 0.0, False, f"fp32 {m}x{k}x{n} splits={splits}")
 
 
+def test_fp32_tma_fed_kernel_gives_the_bits_of_the_register_staged_one(mc, oracle):
+    """The FP32 kernel whose operands arrive through TMA (tensor maps, a 4-stage mbarrier ring; taken whenever A and B
+    are 16-byte aligned with row pitches that are multiples of 4 and a block has at least 512 of K; forced here with
+    variant bit 1024) accumulates every output over K in the order of the register-staged kernel (variant bit 512):
+    identical bits, ragged M, N and K edges and K splits included."""
+    for m, k, n in [(128, 128, 128), (1, 4, 4), (33, 260, 68), (127, 132, 132), (129, 16, 260), (513, 76, 260), (300, 1004, 36),
+                    (256, 2048, 512), (1024, 1024, 1024)]:
+        a = oracle.uniform_values(m * k, 1, -1, 1).reshape(m, k)
+        b = oracle.uniform_values(k * n, 2, -1, 1).reshape(k, n)
+        for splits in [1, 3, 8]:
+            through_tma = _device_gemm(mc, 0, a, b, splits, variant=1024)
+            staged = _device_gemm(mc, 0, a, b, splits, variant=512)
+            assert np.array_equal(through_tma, staged), f"fp32 {m}x{k}x{n} splits={splits}"
+        exact, abs_dot = exact_and_abs(a, b)
+        check_bound(through_tma, exact, abs_dot, k, 0.0, False, f"fp32 tma {m}x{k}x{n}")
+
+
 TC_KINDS = [("tensor_core_bf16", 2, "bf16", 2.0 ** -8, False), ("tensor_core_f16", 3, "f16", 2.0 ** -11, True),
             ("tensor_core_tf32", 1, None, 2.0 ** -11, False)]
 
