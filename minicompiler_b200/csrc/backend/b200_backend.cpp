@@ -882,9 +882,11 @@ private:
         launch->block = kernel.block;
         int blocks_per_sm = 0;
         MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(kernel.block), 0, &blocks_per_sm));
-        const std::size_t wanted = (rows + kernel.rows_per_block - 1) / kernel.rows_per_block;
+        // One block (one cluster of blocks, for rows wider than 8192) per row; the grid is a whole number of clusters.
+        const std::size_t wanted = (rows + kernel.rows_per_block - 1) / kernel.rows_per_block * kernel.cluster;
         std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
         if (options_.eltwise_blocks_per_sm <= 0) resident = wanted;
+        resident = std::max<std::size_t>(kernel.cluster, resident / kernel.cluster * kernel.cluster);
         launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(wanted, resident)));
         launch->pointers.push_back(address(step.result, kRepF32));
         launch->advances.push_back(0);
@@ -920,8 +922,10 @@ private:
         MCD_TRY(mcd_jit_occupancy(launch->function, static_cast<int>(launch->block), 0, &blocks_per_sm));
         std::size_t resident = std::max<std::size_t>(1, static_cast<std::size_t>(blocks_per_sm) * device_.sm_count);
         const std::size_t rows_per_block = launch->block / row_threads(step.reduce_shape.back());
-        const std::size_t wanted = (rows + rows_per_block - 1) / rows_per_block;
+        const std::size_t cluster = row_cluster(step.reduce_shape.back());
+        const std::size_t wanted = (rows + rows_per_block - 1) / rows_per_block * cluster;
         if (options_.eltwise_blocks_per_sm <= 0) resident = wanted;
+        resident = std::max<std::size_t>(cluster, resident / cluster * cluster);
         launch->grid = static_cast<unsigned>(std::max<std::size_t>(1, std::min(wanted, resident)));
         for (NodeId w : step.row_outputs) {
             launch->pointers.push_back(address(w, kRepF32));

@@ -329,7 +329,7 @@ void fuse_row_runs(const Graph& graph, std::vector<Step>* steps) {
             fused.row_parts.push_back(std::move(part));
         }
         // Every full-shaped value costs width / 256 registers per thread while it is live.
-        const std::size_t per_thread = static_cast<std::size_t>((width + row_threads(width) - 1) / row_threads(width));
+        const std::size_t per_thread = static_cast<std::size_t>((row_chunk(width) + row_threads(width) - 1) / row_threads(width));
         if (!ok || fused.row_outputs.empty() || full_values * per_thread > 160) continue;
         fused.result = fused.row_outputs[0];
         steps->erase(steps->begin() + static_cast<std::ptrdiff_t>(lo), steps->begin() + static_cast<std::ptrdiff_t>(hi) + 1);

@@ -23,19 +23,29 @@ namespace minicompiler::cuda {
 inline constexpr const char* kRowReduceKernelName = "mc_row_reduce";
 inline constexpr unsigned kRowReduceBlock = 256;
 
-// Threads that share a row, for both kernels of this file: a warp below 1024 elements (8 rows per 256-thread
-// block), a 256-thread block up to 8192, 512 threads up to 16384 and 1024 up to 32768 (so that a row still fits the
-// registers of the row-fused kernel, 32 per full-shaped value and thread), 256 beyond.
-inline unsigned row_threads(std::int64_t width) {
-    return width < 1024 ? 32u : width <= 8192 ? 256u : width <= 16384 ? 512u : width <= 32768 ? 1024u : 256u;
+// How a row is shared out, for both kernels of this file. Below 1024 elements a warp takes a row (8 rows per
+// 256-thread block). Up to 8192 elements a 256-thread block takes it. Wider rows, up to 65536 elements, are cut into
+// 2, 4 or 8 chunks of at most 8192 columns, one 256-thread CTA each, and those CTAs form a thread-block cluster: every
+// CTA reduces its chunk, the per-CTA results are exchanged through distributed shared memory and combined in rank
+// order by every CTA (the same fixed order in both kernels). Several small CTAs per SM overlap their loads, arithmetic
+// and stores where one 1024-thread block per SM cannot. Beyond 65536 a single 256-thread block loops over the row.
+inline unsigned row_cluster(std::int64_t width) {
+    return width <= 8192 ? 1u : width <= 16384 ? 2u : width <= 32768 ? 4u : width <= 65536 ? 8u : 1u;
 }
-inline unsigned row_block(std::int64_t width) { return row_threads(width) > kRowReduceBlock ? row_threads(width) : kRowReduceBlock; }
+inline unsigned row_threads(std::int64_t width) { return width < 1024 ? 32u : 256u; }
+inline unsigned row_block(std::int64_t width) { (void)width; return 256u; }
+// Columns per CTA of the cluster: whole trips of 256 threads.
+inline std::int64_t row_chunk(std::int64_t width) {
+    const std::int64_t c = row_cluster(width);
+    return c == 1 ? width : ((width + c - 1) / c + 255) / 256 * 256;
+}
 
 struct RowReduceKernel {
     std::string source;
     unsigned threads_per_row = 32;  // row_threads(width)
     unsigned rows_per_block = 8;
     unsigned block = kRowReduceBlock;  // threads per block to launch with
+    unsigned cluster = 1;              // CTAs per row (the kernel carries __cluster_dims__(cluster, 1, 1))
 };
 
 RowReduceKernel generate_row_reduce_kernel(OpKind reduce_op, const FusedProgram& program,
@@ -47,16 +57,17 @@ RowReduceKernel generate_row_reduce_kernel(OpKind reduce_op, const FusedProgram&
 //
 // A run of steps that all work on rows of one shape [.., N] - elementwise steps on the full shape, row reductions,
 // elementwise steps on the reduced [.., 1] values - is generated as ONE kernel: a 256-thread block (a warp, for rows
-// below 1024 elements) owns a row, keeps every full-shaped value in registers (N / 256, or N / 32, elements per
-// thread), gets reduced values by a block (warp) reduction and runs the steps in their original order, so x is read
-// once and y written once (softmax, LayerNorm: two tensor passes instead of four). The reduction order is exactly
-// that of `mc_row_reduce` for the same row length, so a fused run gives the bits of the separate kernels.
+// below 1024 elements; a cluster of 2, 4 or 8 blocks for rows wider than 8192) owns a row, keeps every full-shaped
+// value in registers (at most 32 elements per thread), gets reduced values by a block (warp, cluster) reduction and
+// runs the steps in their original order, so x is read once and y written once (softmax, LayerNorm: two tensor passes
+// instead of four). The reduction order is exactly that of `mc_row_reduce` for the same row length, so a fused run
+// gives the bits of the separate kernels.
 
 namespace minicompiler::cuda {
 
 inline constexpr const char* kRowFusedKernelName = "mc_row_fused";
 inline constexpr std::int64_t kRowFusedMinWidth = 2;     // rows below 1024 elements take one warp, as in mc_row_reduce
-inline constexpr std::int64_t kRowFusedMaxWidth = 32768;  // at most 32 registers per full-shaped value and thread
+inline constexpr std::int64_t kRowFusedMaxWidth = 65536;  // 8 CTAs of 8192 columns: at most 32 registers per full-shaped value and thread
 
 struct RowOperand {
     enum class Kind { Full, PerRow, RowVector, Scalar };

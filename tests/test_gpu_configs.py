@@ -306,7 +306,7 @@ def test_softmax_and_layernorm_against_torch_float64(mc, oracle):
 
     for name, dims in [("x1_softmax", {"M": 64, "N": 1000}), ("x1_softmax", {"M": 16, "N": 8192}), ("x1_softmax", {"M": 9, "N": 20000}),
                        ("x1_softmax", {"M": 3, "N": 40000}), ("x2_layernorm", {"M": 32, "N": 4096}), ("x2_layernorm", {"M": 7, "N": 1023}),
-                       ("x2_layernorm", {"M": 5, "N": 33000})]:
+                       ("x2_layernorm", {"M": 5, "N": 33000}), ("x1_softmax", {"M": 200, "N": 16384}), ("x2_layernorm", {"M": 3, "N": 70000})]:
         # the shipped LayerNorm graph spells 1/N for its default width: write the one of this width
         text = re.sub(r"const inv_n : f32\[\] = \S+", f"const inv_n : f32[] = {1.0 / dims['N']!r}", graph_text(mc, name))
         x = oracle.normal_values(dims["M"] * dims["N"], 7).reshape(dims["M"], dims["N"])

@@ -546,7 +546,8 @@ def test_softmax_and_layernorm_graphs(mc, oracle):
     for name, dims in [("x1_softmax", "M=128,N=1000"), ("x1_softmax", "M=64,N=4096"), ("x2_layernorm", "M=96,N=4096"),
                        ("x1_softmax", "M=300,N=5000"), ("x1_softmax", "M=7,N=8192"), ("x1_softmax", "M=33,N=16384"),
                        ("x1_softmax", "M=1000,N=33"), ("x1_softmax", "M=5,N=1023"), ("x1_softmax", "M=9,N=20000"),
-                       ("x1_softmax", "M=6,N=32768"), ("x2_layernorm", "M=4,N=32768"), ("x1_softmax", "M=3,N=40000")]:
+                       ("x1_softmax", "M=6,N=32768"), ("x2_layernorm", "M=4,N=32768"), ("x1_softmax", "M=3,N=40000"),
+                       ("x1_softmax", "M=300,N=16384"), ("x2_layernorm", "M=5,N=65536"), ("x1_softmax", "M=3,N=70000")]:
         path = mc.graph_path(name)
         g, _ = oracle_inputs(oracle, path=path, dims=dims)
         x = oracle.normal_values(int(np.prod(g.node(g.inputs[0]).shape)), 7)
@@ -555,7 +556,7 @@ def test_softmax_and_layernorm_graphs(mc, oracle):
             got = exe.run([x])[0]
             fused_launches = exe.kernel_launches
         width = int(dims.split("N=")[1])
-        assert fused_launches == (1 if width <= 32768 else 3 if name == "x1_softmax" else fused_launches)  # whole rows in one kernel when they fit in registers
+        assert fused_launches == (1 if width <= 65536 else 3)  # whole rows in one kernel while they fit in registers  # whole rows in one kernel when they fit in registers
         for options in ({"fuse_rows": 0}, {"fuse_rows": 0, "rematerialize": 0}):
             with mc.CompiledGraph(path, dims=dims, options=options) as exe:
                 separate = exe.run([x])[0]

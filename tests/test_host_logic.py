@@ -483,7 +483,7 @@ def test_constant_row_reductions_fold_to_known_answers(mc):
 
 
 def test_row_reduction_lowering_absorbs_and_rematerializes_producers(mc):
-    separate = {"fuse_rows": 0}  # the per-step form; rows of up to 32768 elements otherwise become one kernel
+    separate = {"fuse_rows": 0}  # the per-step form; rows of up to 65536 elements otherwise become one kernel
     g = mc.HostGraph(mc.graph_path("x2_layernorm"), dims="M=64,N=4096")
     plain = g.launch_plan({"rematerialize": 0, **separate})
     assert "row_sum total rows of 4096 prologue_ops=0" in plain
@@ -520,13 +520,18 @@ def test_runs_of_row_steps_become_one_kernel(mc):
     short = mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=1000")
     assert "row_fused" in short.launch_plan({}) and "32 threads per row, 32 element(s) per thread" in short.plan_sources({})
     assert "__syncthreads" not in short.plan_sources({})
+    # rows wider than 8192 are shared by a cluster of 2, 4 or 8 CTAs of 8192 columns at most, in both kernels
     wide = mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=16384")
-    assert "row_fused" in wide.launch_plan({}) and "__launch_bounds__(512)" in wide.plan_sources({})
-    assert "__launch_bounds__(512)" in wide.plan_sources({"fuse_rows": 0})  # the separate reduction shares the row's thread count
-    widest = mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=32768")
-    assert "row_fused" in widest.launch_plan({}) and "__launch_bounds__(1024)" in widest.plan_sources({})
-    assert "1024 threads per row, 32 element(s) per thread" in widest.plan_sources({})
-    assert "row_fused" not in mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=40000").launch_plan({})
+    assert "row_fused" in wide.launch_plan({}) and "__cluster_dims__(2, 1, 1) __launch_bounds__(256)" in wide.plan_sources({})
+    assert "__cluster_dims__(2, 1, 1) __launch_bounds__(256)" in wide.plan_sources({"fuse_rows": 0})
+    widest = mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=65536")
+    assert "row_fused" in widest.launch_plan({}) and "__cluster_dims__(8, 1, 1)" in widest.plan_sources({})
+    assert "256 threads per row, 32 element(s) per thread, 8 CTAs per row as a cluster" in widest.plan_sources({})
+    ragged = mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=20000").plan_sources({})
+    assert "__cluster_dims__(4, 1, 1)" in ragged and "const unsigned chunk_first = rank * 5120u;" in ragged
+    assert "st.shared::cluster.f32" in ragged and "barrier.cluster.arrive.release.aligned" in ragged
+    assert "row_fused" not in mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=70000").launch_plan({})
+    assert "__cluster_dims__" not in mc.HostGraph(mc.graph_path("x1_softmax"), dims="M=64,N=70000").plan_sources({})
     # values that something outside the run reads are written; a matmul ends a run
     text = ("input x : f32[64, 2048]\nconst w : f32[2048, 64] = uniform(seed=3, lo=-1, hi=1)\nm = row_max x\nd = sub x, m\n"
             "e = exp d\ns = row_sum e\ny = div e, s\nz = matmul y, w\noutput z, s")
