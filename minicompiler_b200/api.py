@@ -77,6 +77,7 @@ def lib() -> C.CDLL:
         "mcb_in_place_pointers_ok": (i32, [C.POINTER(vp), i32, i32]),
         "mcd_copy_h2d": (i32, [vp, vp, C.c_size_t, vp]),
         "mcd_copy_d2h": (i32, [vp, vp, C.c_size_t, vp]),
+        "mcd_copy_d2d": (i32, [vp, vp, C.c_size_t, vp]),
         "mcd_device_synchronize": (i32, []),
         "mcd_event_create": (i32, [C.POINTER(vp)]),
         "mcd_event_destroy": (i32, [vp]),
