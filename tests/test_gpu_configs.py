@@ -367,6 +367,35 @@ def test_run_in_row_slices_on_pinned_memory_is_bit_identical(mc, oracle, name, d
         assert np.array_equal(out.numpy(), want)
 
 
+def test_row_slices_move_per_row_columns_and_epilogue_operands_with_their_rows(mc, oracle):
+    """A graph whose cut values include a per-row column that a matmul epilogue reads, a second full-size input added
+    as a residual, an input that is not cut (a row vector) and a row kernel after the matmul: every pointer into a cut
+    tensor has to move with the slice, whatever role the tensor plays in its launch."""
+    import torch
+
+    text = ("input x : f32[8192, 512]\ninput s : f32[8192, 1]\ninput r : f32[8192, 1024]\ninput v : f32[1024]\n"
+            "const w : f32[512, 1024] = uniform(seed=3, lo=-0.05, hi=0.05)\n"
+            "z = matmul x, w\nzs = mul z, s\nzr = add zs, r\nzv = add zr, v\nm = row_max zv\nd = sub zv, m\ny = exp d\noutput y, m")
+    g = oracle.parse_mcg(text)
+    ins = [fast_normal(int(np.prod(g.node(n).shape)), 60 + k) for k, n in enumerate(g.inputs)]
+    for matmul in ("auto", "tensor_core_bf16"):
+        with mc.CompiledGraph(text=text, options={"matmul": matmul, "host_io": 0}) as exe:
+            want = exe.run(ins)
+        pins = [torch.from_numpy(a).pin_memory() for a in ins]
+        outs = [torch.full((w.size,), float("nan"), dtype=torch.float32).pin_memory() for w in want]
+        with mc.CompiledGraph(text=text, options={"matmul": matmul}) as exe:
+            assert exe.row_slices >= 2
+            exe.run_ptrs([p.data_ptr() for p in pins], [o.data_ptr() for o in outs])
+        for got, expect in zip(outs, want):
+            assert np.array_equal(got.numpy(), expect), matmul
+    rows = np.array([0, 511, 512, 4095, 8191])
+    sub = oracle.parse_mcg(text.replace("8192", str(len(rows))))
+    expect = oracle.evaluate_f64(sub, [ins[0].reshape(8192, 512)[rows], ins[1].reshape(8192, 1)[rows], ins[2].reshape(8192, 1024)[rows], ins[3]])
+    with mc.CompiledGraph(text=text) as exe:
+        got = exe.run(ins)
+    assert nse(got[0].reshape(8192, 1024)[rows], expect[0]) <= 1e-4 and nse(got[1].reshape(8192, 1)[rows], expect[1]) <= 1e-4
+
+
 def test_small_or_row_dependent_graphs_are_not_sliced(mc):
     with mc.CompiledGraph(mc.graph_path("c5_mlp_stack"), dims={"B": 256, "D": 256}, options={"matmul": "tensor_core_f16"}) as exe:
         assert exe.row_slices == 0  # moves too little for the overlap to pay
