@@ -84,6 +84,18 @@ def algorithmic_work(oracle, graph, kind):
     return flops
 
 
+def matmul_operand_bytes(graph, elem_bytes):
+    """Bytes a matmul graph must move at least: each matmul's two operands once in the arithmetic's operand width and
+    its FP32 result once (2(mk + kn) + 4mn for 16-bit operands). Used to tell whether HBM or the math bounds a shape."""
+    total = 0
+    for n in graph.nodes:
+        if n.op == "matmul":
+            a, b = graph.node(n.operands[0]), graph.node(n.operands[1])
+            m, k, nn = a.shape[0], a.shape[1], b.shape[1]
+            total += elem_bytes * (m * k + k * nn) + 4 * m * nn
+    return total
+
+
 def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -395,6 +407,7 @@ def main():
         peaks = measured_peaks()
         median_ms = per_step[len(per_step) // 2]
         avg_ms = total_ms / steps
+        min_bytes = 0
         if kind == "bytes":
             achieved = work_rank / (avg_ms * 1e-3) / 1e9
             peak, unit, bound = peaks["hbm_gbs"], "GB/s", "hbm"
@@ -407,6 +420,13 @@ def main():
             unit, bound = "TFLOP/s", "tensor" if matmul != "auto" else "fp32-fma"
             peak_kind = ("FP32 FMA peak at the maximum SM clock (2 x 148 SMs x 128 lanes x 1965 MHz)" if matmul == "auto" else
                          ("sustained" if sustained else "burst") + " cuBLAS bf16 GEMM" + (", halved for TF32" if DTYPES[matmul] == "tf32" else ""))
+            # A shape whose arithmetic intensity lies below the ridge of the two peaks is bound by streaming its
+            # operands, not by the math: its roofline is the HBM one (skinny matmuls: 16 or 128 rows against 8192^2).
+            min_bytes = matmul_operand_bytes(g, 4 if DTYPES[matmul] in ("f32", "tf32") else 2)
+            if min_bytes > 0 and work_rank / min_bytes < peak * 1e12 / (peaks["hbm_gbs"] * 1e9):
+                achieved = min_bytes / (avg_ms * 1e-3) / 1e9
+                peak, unit, bound = peaks["hbm_gbs"], "GB/s", "hbm"
+                peak_kind = "copy bandwidth (operands once + FP32 result once; intensity below the ridge)"
         traffic = None
         tfile = ROOT / "profiles" / "ncu_traffic.json"
         if tfile.exists():
@@ -417,7 +437,8 @@ def main():
         roofline = {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                     "traffic": traffic, "peak_source": f"of {peaks['source']}: {peak_kind}",
                     "kernel_ms_avg": avg_ms / max(1, launches_per_step), "step_ms_median": median_ms,
-                    "launches_per_step": launches_per_step, "algorithmic_per_launch": work_rank / max(1, launches_per_step),
+                    "launches_per_step": launches_per_step,
+                    "algorithmic_per_launch": (min_bytes if (kind == "flops" and bound == "hbm") else work_rank) / max(1, launches_per_step),
                     "kernels": exe.matmul_kernels if kind == "flops" else ["mc_elementwise (generated)"]}
 
         cpu = None
