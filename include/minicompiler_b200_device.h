@@ -103,6 +103,11 @@ MCD_API int mcd_launch(void* function, unsigned grid_x, unsigned grid_y, unsigne
 /* The same with thread-block clusters of `cluster_x` CTAs along x (grid_x a multiple of it). */
 MCD_API int mcd_launch_cluster(void* function, unsigned grid_x, unsigned cluster_x, unsigned block_x, size_t dynamic_smem,
                                void* stream, void** params);
+/* Launch as a programmatic dependent of the kernel launched before it on `stream`: the blocks may become resident
+ * while that kernel drains (once all of its CTAs have executed griddepcontrol.launch_dependents or exited); the
+ * kernel must execute griddepcontrol.wait before it touches what its predecessor wrote. */
+MCD_API int mcd_launch_dependent(void* function, unsigned grid_x, unsigned block_x, size_t dynamic_smem, void* stream,
+                                 void** params);
 /* Launch-list replay (the reference names CUDA-graph replay of enqueue as its next step, README.md:554-556).
  * Between begin and end every launch issued on `stream` through this layer is recorded instead of run;
  * end returns an executable graph that mcd_graph_launch replays on any stream of the same device. */

@@ -572,6 +572,28 @@ int mcd_launch_cluster(void* function, unsigned grid_x, unsigned cluster_x, unsi
     return check_drv(drv->LaunchKernelEx(&config, static_cast<CUfunction>(function), params, nullptr), "cuLaunchKernelEx");
 }
 
+int mcd_launch_dependent(void* function, unsigned grid_x, unsigned block_x, size_t dynamic_smem, void* stream, void** params) {
+    const DriverApi* drv = driver_api();
+    if (drv == nullptr) return fail("the CUDA driver API is unavailable");
+    CUlaunchAttribute attribute;
+    attribute.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+    attribute.value.programmaticStreamSerializationAllowed = 1;
+    CUlaunchConfig config;
+    std::memset(&config, 0, sizeof config);
+    config.gridDimX = grid_x;
+    config.gridDimY = 1;
+    config.gridDimZ = 1;
+    config.blockDimX = block_x;
+    config.blockDimY = 1;
+    config.blockDimZ = 1;
+    config.sharedMemBytes = static_cast<unsigned>(dynamic_smem);
+    config.hStream = static_cast<CUstream>(stream);
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return check_drv(drv->LaunchKernelEx(&config, static_cast<CUfunction>(function), params, nullptr), "cuLaunchKernelEx");
+}
+
 // ------------------------------------------------------------ graph replay
 
 namespace {

@@ -88,6 +88,9 @@ __device__ __forceinline__ void mc_gemm_f32_body(const float* __restrict__ A, co
     const int n0 = blockIdx.x * MC_F32_BN;
     const int k_begin = blockIdx.z * k_per_split;
     const int k_end = min(K, k_begin + k_per_split);
+    // With K split, the reduction kernel that follows may take its places while this grid drains (it waits for this
+    // grid to complete before it reads the partial sums).
+    if (gridDim.z > 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // Global -> register staging coordinates.
     // 0..63 (and +64). The two upper k-groups of a lane quad take the row 8 further on, so that the transposed
@@ -248,6 +251,7 @@ mc_gemm_f32_tma(const __grid_constant__ McTensorMap map_a, const __grid_constant
     const int k_begin = blockIdx.z * k_per_split;
     const int k_end = min(K, k_begin + k_per_split);
     const int steps = (k_end - k_begin + MC_F32_BK - 1) / MC_F32_BK;
+    if (gridDim.z > 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (tid == 0) {
         abort_flag_storage = 0;

@@ -199,9 +199,27 @@ int reduce_splits(const mcd_gemm_args* a, int splits, cudaStream_t s) {
     auto* c16 = static_cast<unsigned short*>(a->c16);
     int kind = a->c16_kind, m = a->m, n = a->n;
     long long ldc = a->ldc, ldc16 = a->ldc16;
+    // A programmatic dependent of the matmul launched just before it: its blocks take their places while the matmul
+    // drains and wait (griddepcontrol.wait) until the partial sums are complete. Variant bit 2048: a plain launch.
+    const bool dependent = (a->variant & 2048) == 0;
     if (a->reduce_function != nullptr) {
         void* params[] = {&ws, &c, &c16, &kind, &m, &n, &ldc, &ldc16, &splits, &epi};
+        if (dependent) return mcd_launch_dependent(a->reduce_function, grid, 256, 0, s, params);
         return mcd_launch(a->reduce_function, grid, 1, 1, 256, 0, s, params);
+    }
+    if (dependent) {
+        cudaLaunchAttribute attribute;
+        attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute.val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(grid, 1, 1);
+        config.blockDim = dim3(256, 1, 1);
+        config.stream = s;
+        config.attrs = &attribute;
+        config.numAttrs = 1;
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return check_rt(cudaLaunchKernelEx(&config, mc_splitk_reduce, ws, c, c16, kind, m, n, ldc, ldc16, splits, epi),
+                        "cudaLaunchKernelEx(mc_splitk_reduce, dependent)");
     }
     mc_splitk_reduce<<<grid, 256, 0, s>>>(ws, c, c16, kind, m, n, ldc, ldc16, splits, epi);
     return launched("mc_splitk_reduce");

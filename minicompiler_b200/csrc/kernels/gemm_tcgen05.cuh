@@ -246,6 +246,10 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // When K is split, the reduction kernel that follows is launched as a programmatic dependent: once every CTA of
+    // this grid has passed this point its blocks may take their places (they wait for this grid to complete before
+    // they read anything), which hides its launch latency behind the main loop.
+    if (p.splits > 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const int tiles_m = (p.m + MC_TC_BM - 1) / MC_TC_BM;
     const int bn = p.tile_n;  // columns per tile; accumulators stay MC_TC_BN TMEM columns apart

@@ -6,6 +6,9 @@
 extern "C" __global__ void __launch_bounds__(256)
 mc_splitk_reduce(const float* __restrict__ workspace, float* __restrict__ C, unsigned short* __restrict__ C16,
                  int c16_kind, int M, int N, long long ldc, long long ldc16, int splits, McEpilogueArgs epi) {
+    // Launched as a programmatic dependent of the matmul that wrote the partial sums: its blocks may already be
+    // resident while that grid drains, and wait here until it has completed and its writes are visible.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const long long slice = (long long)M * N;
     const bool vec = (N & 3) == 0 && (ldc & 3) == 0 && ((unsigned long long)C & 15) == 0 &&
                      ((unsigned long long)workspace & 15) == 0;
