@@ -152,6 +152,10 @@ MC_EXPORT int mcb_graph_plan_sources(const void* graph, const char* options, int
 MC_EXPORT int mcb_in_place_pointers_ok(const void* const* pointers, int count, int any_vectorized);
 MC_EXPORT void mcb_uniform_values(float* out, long long count, unsigned long long seed, float lo, float hi);
 MC_EXPORT int mcb_split_k_splits(int m, int n, int k, int sm_count, int blocks_per_sm);
+/* K splits `auto` adds on B200 to an FP32 problem the reference's rule leaves whole, when its 128 x 128 tiles share
+ * out badly over the SMs (1 = none); no counterpart in the reference, whose rule was calibrated on one 30-SM GPU
+ * (README.md:557-560). */
+MC_EXPORT int mcb_balanced_fp32_splits(int m, int n, int k, int sm_count);
 MC_EXPORT int mcb_tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes);
 /* Columns per tile (256, 128 or 64) the tcgen05 path uses for an unsplit m x n x k problem; no counterpart in the
  * reference, whose tensor-core kernel has one tile shape (src/cuda/matmul_tensor_core.cu:27-35). */

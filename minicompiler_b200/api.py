@@ -110,6 +110,7 @@ def lib() -> C.CDLL:
         "mcb_uniform_values": (None, [C.POINTER(C.c_float), i64, C.c_ulonglong, C.c_float, C.c_float]),
         "mcb_split_k_splits": (i32, [i32, i32, i32, i32, i32]),
         "mcb_tensor_core_splits": (i32, [i32, i32, i32, i32, i32]),
+        "mcb_balanced_fp32_splits": (i32, [i32, i32, i32, i32]),
         "mcb_tensor_core_tile_n": (i32, [i32, i32, i32, i32, i32]),
         "mcb_resolve_matmul_kernel": (cp, [cp, i32, i32, i32, i32]),
         "mcd_launch_count": (C.c_ulonglong, []),

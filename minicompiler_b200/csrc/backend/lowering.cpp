@@ -1,6 +1,7 @@
 #include "backend/lowering.hpp"
 
 #include <algorithm>
+#include <cmath>
 #include <array>
 #include <cstdio>
 #include <sstream>
@@ -89,6 +90,33 @@ int tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes) {
     const std::int64_t k_blocks = (k + block_k - 1) / block_k;
     std::int64_t splits = std::min<std::int64_t>(sms / tiles, k_blocks / 4);  // at least 4 K blocks per work item
     return static_cast<int>(std::max<std::int64_t>(splits, 1));
+}
+
+int balanced_fp32_splits(int m, int n, int k, int sm_count) {
+    const std::int64_t tiles = ((static_cast<std::int64_t>(m) + 127) / 128) * ((static_cast<std::int64_t>(n) + 127) / 128);
+    // Work is shared out in whole blocks: with `items` equal blocks an SM gets ceil(items / SMs) of them at worst.
+    auto efficiency = [&](std::int64_t items) {
+        const double per_sm = static_cast<double>(items) / sm_count;
+        return per_sm / std::ceil(per_sm);
+    };
+    const double unsplit = efficiency(tiles);
+    if (unsplit >= 0.9) return 1;
+    // Seconds: the matmul at the kernel's measured rate, and the reduction that a split adds (it reads `splits`
+    // partial results and writes one, plus a launch).
+    const double main_s = 2.0 * m * n * static_cast<double>(k) / 50e12 / unsplit;
+    int best = 1;
+    double best_gain = 0.03;
+    for (int splits : {2, 3, 4, 6, 8}) {
+        if (k / splits < 256) break;
+        const double reduce_s = (splits + 1) * 4.0 * m * n / 5e12 + 4e-6;
+        const double total_s = main_s * unsplit / efficiency(tiles * splits) + reduce_s;
+        const double gain = main_s / total_s - 1.0;
+        if (gain > best_gain) {
+            best_gain = gain;
+            best = splits;
+        }
+    }
+    return best;
 }
 
 bool tensor_core_cluster_reduce(int k, int elem_bytes, int splits, int tile_n, int gemm_variant) {
@@ -440,12 +468,19 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
         if (kernel == MatmulKernel::TensorCoreTf32 && (s.k % 4 != 0 || s.n % 4 != 0)) {
             kernel = resolve_matmul_kernel(MatmulKernel::Auto, s.m, s.n, s.k, sm_count);
         }
+        // `auto` on a problem the reference's rule leaves whole: split K after all when whole tiles would leave SMs
+        // idle for a good part of the launch and finer work items share out evenly.
+        int balanced = 1;
+        if (options.matmul == MatmulKernel::Auto && kernel == MatmulKernel::DoubleBuffered && options.balance_splits) {
+            balanced = balanced_fp32_splits(s.m, s.n, s.k, sm_count);
+            if (balanced > 1) kernel = MatmulKernel::SplitK;
+        }
         s.kernel = kernel;
         s.arith = kernel == MatmulKernel::TensorCoreTf32   ? Arith::Tf32
                   : kernel == MatmulKernel::TensorCoreBf16 ? Arith::Bf16
                   : kernel == MatmulKernel::TensorCoreF16  ? Arith::F16
                                                            : Arith::F32;
-        s.splits = matmul_splits(kernel, s.m, s.n, s.k, sm_count);
+        s.splits = balanced > 1 ? balanced : matmul_splits(kernel, s.m, s.n, s.k, sm_count);
         if (is_tensor_core(kernel)) {
             s.tile_n = tensor_core_tile_n(s.m, s.n, s.k, sm_count, kernel == MatmulKernel::TensorCoreTf32 ? 4 : 2);
         }

@@ -46,6 +46,11 @@ bool uses_split_k(MatmulKernel kernel);
 // The reference's split rule, from the count of 128x128 output tiles
 // (src/cuda/matmul_kernels.cu:352-367); its tests pin known answers for 30 SMs.
 int split_k_splits(int m, int n, int k, int sm_count, int blocks_per_sm = 2);
+// Beyond the reference's rule, for `auto` on B200: a problem whose 128x128 tiles cover the SMs but share out badly
+// (256 tiles on 148 SMs: two on most, one on the rest, 0.86 of the time useful) is split along K when finer work
+// items share out evenly and the reduction costs less than that gains (2048^3: 4 splits, 398 -> 349 us measured).
+// Returns the split count, 1 to leave the problem whole.
+int balanced_fp32_splits(int m, int n, int k, int sm_count);
 // The rule for the tcgen05 kernels: 128x256 tiles, one persistent CTA per SM.
 int tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes);
 // Columns per tile of the one-CTA tcgen05 kernel for this problem: 256, or 128 / 64 for problems that neither fill
@@ -92,6 +97,7 @@ struct CudaOptions {
     int host_io_row_slices = 16;  // same for row-independent graphs with matmuls or row kernels (0 turns that path off)
     bool fuse_rows = true;      // runs of steps on rows of one shape become one kernel (reduce_codegen.hpp)
     bool rematerialize = true;  // recompute cheap elementwise values read by a row reduction in each reader
+    bool balance_splits = true; // `auto`: split K of FP32 matmuls whose whole tiles share out badly over the SMs
 };
 
 enum class Arith : int { F32 = 0, Tf32 = 1, Bf16 = 2, F16 = 3 };  // same numbering as MCD_GEMM_*

@@ -120,6 +120,8 @@ Status parse_options(const char* text, cuda::CudaOptions* options) {
                 options->host_io_slices = static_cast<int>(number);
             } else if (key == "host_io_row_slices") {
                 options->host_io_row_slices = static_cast<int>(number);
+            } else if (key == "balance_splits") {
+                options->balance_splits = number != 0;
             } else if (key == "fuse_rows") {
                 options->fuse_rows = number != 0;
             } else if (key == "rematerialize") {
@@ -134,7 +136,7 @@ Status parse_options(const char* text, cuda::CudaOptions* options) {
                 options->eltwise_blocks_per_sm = static_cast<int>(number);
             } else {
                 return Error{"unknown option '" + key +
-                             "' (device, matmul, vectorize, fuse_epilogue, b_layout, unroll, streaming, gemm_variant, fmad, blocks_per_sm, graph, host_io, host_io_slices, host_io_row_slices, rematerialize, fuse_rows)"};
+                             "' (device, matmul, vectorize, fuse_epilogue, b_layout, unroll, streaming, gemm_variant, fmad, blocks_per_sm, graph, host_io, host_io_slices, host_io_row_slices, rematerialize, fuse_rows, balance_splits)"};
             }
         }
     }
@@ -663,6 +665,8 @@ void mcb_uniform_values(float* out, long long count, unsigned long long seed, fl
 int mcb_split_k_splits(int m, int n, int k, int sm_count, int blocks_per_sm) {
     return cuda::split_k_splits(m, n, k, sm_count, blocks_per_sm);
 }
+
+int mcb_balanced_fp32_splits(int m, int n, int k, int sm_count) { return cuda::balanced_fp32_splits(m, n, k, sm_count); }
 
 int mcb_tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes) {
     return cuda::tensor_core_splits(m, n, k, sm_count, elem_bytes);

@@ -675,3 +675,20 @@ def test_split_tensor_core_matmuls_that_reduce_in_a_cluster_need_one_launch_and_
         assert "splits=4" in plan and "launches=1\n" in plan and "workspace_bytes=0" in plan, plan
         plan = mc.HostGraph(text=text, dims={"M": m, "N": n, "K": k}).launch_plan({"matmul": "tensor_core_bf16"})
         assert "splits=4" in plan and "launches=2\n" in plan
+
+
+def test_auto_splits_k_where_whole_tiles_share_out_badly(mc):
+    """Beyond the reference's rule (kept verbatim, pinned above): on 148 SMs a problem of 256 or 512 tiles of 128 x 128
+    leaves SMs idle 14 % of the launch; `auto` then splits K so that finer work items share out evenly - when K is long
+    enough and the reduction costs less than that gains."""
+    b = mc.lib().mcb_balanced_fp32_splits
+    assert b(2048, 2048, 2048, 148) == 4 and b(8192, 1024, 4096, 148) == 2
+    assert b(4096, 4096, 4096, 148) == 1 and b(8192, 4096, 1024, 148) == 1 and b(65536, 2048, 2048, 148) == 1
+    assert b(2048, 2048, 256, 148) == 1  # K too short to split
+    text = "dim M = 8\ndim N = 8\ndim K = 8\ninput a : f32[M, K]\ninput b : f32[K, N]\nc = matmul a, b\noutput c"
+    plan = mc.HostGraph(text=text, dims={"M": 2048, "N": 2048, "K": 2048}).launch_plan()
+    assert "kernel=split_k splits=4" in plan and "launches=2" in plan
+    assert "kernel=double_buffered splits=1" in mc.HostGraph(text=text, dims={"M": 2048, "N": 2048, "K": 2048}).launch_plan({"balance_splits": 0})
+    assert "kernel=double_buffered splits=1" in mc.HostGraph(text=text, dims={"M": 2048, "N": 2048, "K": 2048}).launch_plan({"matmul": "double_buffered"})
+    c3 = mc.HostGraph(mc.graph_path("c3_ffn")).launch_plan()
+    assert "matmul z 8192x4096x1024 kernel=double_buffered splits=1" in c3 and "matmul o 8192x1024x4096 kernel=split_k splits=2" in c3
