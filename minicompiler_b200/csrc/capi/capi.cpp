@@ -650,7 +650,10 @@ int mcb_graph_plan_sources(const void* graph, const char* options, int sm_count,
     for (std::size_t i = 0; i < lowered->steps.size(); ++i) {
         const cuda::Step& step = lowered->steps[i];
         if (step.kind == cuda::Step::Kind::Matmul) {
-            if (step.has_epilogue) text += "// step " + std::to_string(i) + "\n" + cuda::generate_epilogue_source(g, step) + "\n";
+            if (step.has_epilogue) {
+                text += "// step " + std::to_string(i) + ": epilogue of matmul '" + g.node(step.matmul).name + "' computing '" +
+                        g.node(step.result).name + "'\n" + cuda::generate_epilogue_source(g, step) + "\n";
+            }
             continue;
         }
         text += "// step " + std::to_string(i) + "\n" + step_source(g, parsed, step) + "\n";
