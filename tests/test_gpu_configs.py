@@ -396,6 +396,25 @@ def test_row_slices_move_per_row_columns_and_epilogue_operands_with_their_rows(m
     assert nse(got[0].reshape(8192, 1024)[rows], expect[0]) <= 1e-4 and nse(got[1].reshape(8192, 1)[rows], expect[1]) <= 1e-4
 
 
+def test_row_slices_with_an_output_that_later_layers_also_read(mc, oracle):
+    """The MLP stack with a middle activation as a second output: that value is written in FP32 (for the caller, outside
+    the buffer pool) and in 16 bits (for the next layer, inside it) by the same launch; both forms move with the slice."""
+    import torch
+
+    dims = {"B": 8192, "D": 1024}
+    text = with_outputs(graph_text(mc, "c5_mlp_stack"), ["a3", "a7"])
+    x = fast_normal(8192 * 1024, 77)
+    with mc.CompiledGraph(text=text, dims=dims, options={"matmul": "tensor_core_f16", "host_io": 0}) as exe:
+        want = exe.run([x])
+    pin = torch.from_numpy(x).pin_memory()
+    outs = [torch.full((w.size,), float("nan"), dtype=torch.float32).pin_memory() for w in want]
+    with mc.CompiledGraph(text=text, dims=dims, options={"matmul": "tensor_core_f16"}) as exe:
+        assert exe.row_slices >= 2
+        exe.run_ptrs([pin.data_ptr()], [o.data_ptr() for o in outs])
+    for got, expect in zip(outs, want):
+        assert np.array_equal(got.numpy(), expect)
+
+
 def test_small_or_row_dependent_graphs_are_not_sliced(mc):
     with mc.CompiledGraph(mc.graph_path("c5_mlp_stack"), dims={"B": 256, "D": 256}, options={"matmul": "tensor_core_f16"}) as exe:
         assert exe.row_slices == 0  # moves too little for the overlap to pay
