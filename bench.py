@@ -269,6 +269,12 @@ def main():
     if args.also == "none":
         args.also = ""
 
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+        # Started by hand for several GPUs: one rank per GPU is what torch.distributed.run sets up.
+        os.execvp(sys.executable, [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(args.gpus),
+                                   "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29500"),
+                                   str(Path(__file__).resolve()), *sys.argv[1:]])
+
     if args.impl == "reference":
         run_reference_arm(args)
         return
