@@ -750,8 +750,11 @@ private:
             slicing_ = RowSlicing{};
             return Status();
         }
-        // The largest slice count up to the requested one that divides the rows into multiples of 128 (whole tiles).
-        for (std::int64_t slices = options_.host_io_row_slices; slices >= 2; --slices) {
+        // The largest slice count up to the requested one that divides the rows into multiples of 128 (whole tiles)
+        // and leaves every slice at least 16 MiB to move: smaller copies cost more at the stream hand-offs than
+        // shorter ends save.
+        const std::int64_t most = std::min<std::int64_t>(options_.host_io_row_slices, static_cast<std::int64_t>(moved / kMinSliceBytes));
+        for (std::int64_t slices = most; slices >= 2; --slices) {
             if (slicing_.rows % slices == 0 && (slicing_.rows / slices) % 128 == 0) {
                 slice_rows_ = slicing_.rows / slices;
                 break;
@@ -1055,6 +1058,7 @@ private:
     // Row slicing of run() on pinned memory: the analysis, the rows per slice (0 = off), the graph and plan at
     // that row count, and its launches, which use the full plan's addresses and are moved row-wise per slice.
     static constexpr std::size_t kMinSlicedBytes = std::size_t{32} << 20;
+    static constexpr std::size_t kMinSliceBytes = std::size_t{16} << 20;
     RowSlicing slicing_;
     std::int64_t slice_rows_ = 0;
     Graph slice_graph_;
