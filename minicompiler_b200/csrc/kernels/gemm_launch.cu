@@ -497,11 +497,36 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
         p.half_tiles = ((a->variant & 2) == 0 && pair_tail > 0 && 2 * pair_tail <= clusters) ? pair_tail : 0;
         const int items = pair_tiles + p.half_tiles;
         const unsigned pair_grid = 2u * static_cast<unsigned>(std::max(1, std::min(items, clusters)));
+        // Outputs leave as TMA stores of 32 x 32 boxes out of each warp's staging buffer (128-byte rows of FP32 with the
+        // 128-byte swizzle, 64-byte rows of 16-bit values with the 64-byte swizzle) when a tensor map can describe them:
+        // 16-byte aligned bases and row pitches. Otherwise the kernel stores directly from registers.
+        McTensorMap map_c, map_c16;
+        std::memset(&map_c, 0, sizeof(map_c));
+        std::memset(&map_c16, 0, sizeof(map_c16));
+        const bool c_ok = a->c == nullptr || (aligned16(a->c) && a->ldc % 4 == 0);
+        const bool c16_ok = a->c16 == nullptr || (aligned16(a->c16) && a->ldc16 % 8 == 0);
+        if (p.staged != 0 && c_ok && c16_ok) {
+            if (a->c != nullptr) {
+                if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_c), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a->c, a->n, a->m,
+                                        a->ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
+                    return rc;
+                }
+            }
+            if (a->c16 != nullptr) {
+                if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_c16), CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a->c16, a->n,
+                                        a->m, a->ldc16, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B)) {
+                    return rc;
+                }
+            }
+        } else {
+            p.staged = 0;
+        }
         if (a->function != nullptr) {
-            void* params[] = {&map_a, &map_b, &p, &epi};
+            void* params[] = {&map_a, &map_b, &map_c, &map_c16, &p, &epi};
             return mcd_launch(a->function, pair_grid, 1, 1, MC_TC_THREADS, MC_TC2_SMEM_BYTES, s, params);
         }
-        using PairKernel = void (*)(const McTensorMap, const McTensorMap, const McTcParams, const McEpilogueArgs);
+        using PairKernel = void (*)(const McTensorMap, const McTensorMap, const McTensorMap, const McTensorMap, const McTcParams,
+                                    const McEpilogueArgs);
         PairKernel kernel = p.wide ? (tf32 ? mc_gemm_tc2w_tf32_bk : (b_k_major ? mc_gemm_tc2w_h16_bk : mc_gemm_tc2w_h16_bmn))
                                    : (tf32 ? mc_gemm_tc2_tf32_bk : (b_k_major ? mc_gemm_tc2_h16_bk : mc_gemm_tc2_h16_bmn));
         // The opt-in to more than 48 KB of dynamic shared memory is kept per device.
@@ -517,7 +542,7 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
                 }
             }
         }
-        kernel<<<pair_grid, MC_TC_THREADS, MC_TC2_SMEM_BYTES, s>>>(map_a, map_b, p, epi);
+        kernel<<<pair_grid, MC_TC_THREADS, MC_TC2_SMEM_BYTES, s>>>(map_a, map_b, map_c, map_c16, p, epi);
         return launched("mc_gemm_tc2");
     }
 

@@ -23,7 +23,9 @@
 #define MC_TC2_B_BYTES (128 * 128)
 #define MC_TC2_STAGE_BYTES (MC_TC2_A_BYTES + MC_TC2_B_BYTES)
 #define MC_TC2_STAGING_PER_WARP 4096
-#define MC_TC2_SMEM_BYTES (MC_TC2_STAGES * MC_TC2_STAGE_BYTES + 1024 + 256 + MC_TC_EPILOGUE_WARPS * MC_TC2_STAGING_PER_WARP)
+#define MC_TC2_BARRIER_BYTES 1024  // keeps the staging buffers behind the barriers 1024-byte aligned (128-byte swizzle)
+#define MC_TC2_SMEM_BYTES \
+    (MC_TC2_STAGES * MC_TC2_STAGE_BYTES + 1024 + MC_TC2_BARRIER_BYTES + MC_TC_EPILOGUE_WARPS * MC_TC2_STAGING_PER_WARP)
 
 // TMA load whose completion is counted on a barrier that may sit in the peer CTA of the pair.
 __device__ __forceinline__ void mc_tma_load_2d_pair(unsigned smem_dst, const McTensorMap* map, unsigned bar_cluster_addr, int c0,
@@ -34,14 +36,27 @@ __device__ __forceinline__ void mc_tma_load_2d_pair(unsigned smem_dst, const McT
         : "memory");
 }
 
-__device__ __forceinline__ void mc_st_shared_v4(unsigned addr, float a, float b, float c, float d) {
-    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+// TMA store of one box from shared memory; completion is tracked in the issuing thread's bulk groups. Rows and
+// columns of the box that lie outside the tensor are not written.
+__device__ __forceinline__ void mc_tma_store_2d(const McTensorMap* map, unsigned smem_src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"((unsigned long long)map),
+                 "r"(smem_src), "r"(c0), "r"(c1)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
-__device__ __forceinline__ float4 mc_ld_shared_v4(unsigned addr) {
-    float4 v;
-    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
-    return v;
+// Until the bulk stores this thread has issued have read their shared-memory source.
+__device__ __forceinline__ void mc_tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
+// Shared-memory writes of this thread become visible to the TMA unit.
+__device__ __forceinline__ void mc_fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void mc_st_shared_v4u(unsigned addr, unsigned a, unsigned b, unsigned c, unsigned d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+__device__ __forceinline__ void mc_st_shared_v4(unsigned addr, float a, float b, float c, float d) {
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 __device__ __forceinline__ void mc_umma_pair(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b, unsigned idesc,
@@ -75,8 +90,8 @@ __device__ __forceinline__ void mc_umma_commit_pair(unsigned bar) {
 }
 
 template <int kElemBytes, bool kBIsKMajor, bool kWide>
-__device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const McTensorMap& map_b, const McTcParams& p,
-                                                 const McEpilogueArgs& epi) {
+__device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const McTensorMap& map_b, const McTensorMap& map_c,
+                                                 const McTensorMap& map_c16, const McTcParams& p, const McEpilogueArgs& epi) {
     constexpr int kBlockK = 128 / kElemBytes;
     constexpr int kMmaK = 32 / kElemBytes;
     constexpr int kMmasPerBlock = kBlockK / kMmaK;
@@ -334,7 +349,7 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
         const bool vec16 = (p.ldc16 & 7) == 0 && (((unsigned long long)p.c16) & 15) == 0;
         // Staged stores need the aligned fast paths of both outputs; anything else takes the direct per-row stores.
         const bool staged = p.staged != 0 && (p.c == nullptr || vec4) && (p.c16 == nullptr || vec16);
-        const unsigned stage_base = bars_base + 256 + (unsigned)(warp - 2) * MC_TC2_STAGING_PER_WARP;
+        const unsigned stage_base = bars_base + MC_TC2_BARRIER_BYTES + (unsigned)(warp - 2) * MC_TC2_STAGING_PER_WARP;
         int acc = 0;
         unsigned full_phase = 0;  // bit r: parity of region r's tmem_full barrier
         bool ok = true;
@@ -357,27 +372,32 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int n0 = (nb + s) * MC_TC_BN;
-                // The warp's whole slice of the region goes to registers at once and the region is handed back to
-                // the MMA issuer before any arithmetic or store, so those overlap the next tile's MMAs.
-                unsigned v[kColsPerWarp / 32][32];
+                // The warp reads its slice of the region 32 columns at a time and finishes each piece (arithmetic,
+                // staging, stores) before it asks for the next. Reading the whole slice at once was measured to stall
+                // the next tile's MMAs for as long as the reads take (2.4 us per 256 x 256 tile, whatever K is):
+                // 32 TMEM loads issued together by the 8 warps hold up the MMAs behind them, 8 at a time do not. The
+                // region goes back to the MMA issuer when the last piece is in registers.
+                int last_chunk = -1;
 #pragma unroll
                 for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {
-                    if (chunk * 32 < warp_cols) {
-                        mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(r * MC_TC_BN + acc_col_begin + chunk * 32),
-                                       v[chunk]);
-                    }
+                    if (chunk * 32 < warp_cols) last_chunk = chunk;
                 }
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mc_mbar_arrive_cluster(mc_mapa(bar_tmem_empty + 8 * r, 0));
 #pragma unroll
                 for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {
+                    if (chunk * 32 >= warp_cols) continue;  // warp-uniform
+                    unsigned v[32];
+                    mc_tmem_load32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(r * MC_TC_BN + acc_col_begin + chunk * 32), v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (chunk == last_chunk) {
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mc_mbar_arrive_cluster(mc_mapa(bar_tmem_empty + 8 * r, 0));
+                    }
                     const int col0 = n0 + tile_col_begin + chunk * 32;
-                    if (chunk * 32 >= warp_cols || col0 >= p.n) continue;  // warp-uniform
+                    if (col0 >= p.n) continue;  // warp-uniform
                     float f[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[chunk][j]);
+                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
                     const bool whole_chunk = col0 + 32 <= p.n;
                     if (row < p.m) {
                         if (whole_chunk) {
@@ -389,45 +409,41 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                             }
                         }
                     }
-                    if (staged && whole_chunk) {
-                        // The 32 x 32 block goes through shared memory (16-byte pieces XOR-swizzled by row, so both
-                        // directions run at 4 wavefronts per 512 bytes) and leaves as whole 128-byte (FP32) or 64-byte
-                        // (16-bit) row segments: 4 or 8 complete rows per store instruction instead of 32 pieces.
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            mc_st_shared_v4(stage_base + lane * 128 + ((j ^ (lane & 7)) << 4), f[4 * j], f[4 * j + 1], f[4 * j + 2],
-                                            f[4 * j + 3]);
-                        }
-                        __syncwarp();
+                    if (staged) {
+                        // The 32 x 32 block is written to this warp's staging buffer in the layout a swizzled TMA box
+                        // has (16-byte pieces XOR-ed with the row number: no bank conflicts) and leaves as ONE TMA store:
+                        // the data never passes through the load/store unit again. Plain vector stores from the
+                        // 8 warps were measured to hold up the MMAs of the next tile by 1.5 us per 256 x 256 tile (the
+                        // same kernel with the stores left out, or with the TMEM reads alone, ran at the MMA rate).
+                        // TMA writes only the part of the box that lies inside the tensor, so ragged edges need no care.
                         if (p.c != nullptr) {
+                            if (lane == 0) mc_tma_store_wait_read();  // the previous box has left the buffer
+                            __syncwarp();
 #pragma unroll
-                            for (int q = 0; q < 8; ++q) {
-                                const int rr = q * 4 + (lane >> 3);
-                                const int cc = lane & 7;
-                                const float4 piece = mc_ld_shared_v4(stage_base + rr * 128 + ((cc ^ (rr & 7)) << 4));
-                                if (row_base + rr < p.m) {
-                                    *reinterpret_cast<float4*>(p.c + (long long)(row_base + rr) * p.ldc + col0 + cc * 4) = piece;
-                                }
+                            for (int j = 0; j < 8; ++j) {
+                                mc_st_shared_v4(stage_base + lane * 128 + ((j ^ (lane & 7)) << 4), f[4 * j], f[4 * j + 1], f[4 * j + 2],
+                                                f[4 * j + 3]);
                             }
+                            mc_fence_async_shared();
+                            __syncwarp();
+                            if (lane == 0) mc_tma_store_2d(&map_c, stage_base, col0, row_base);
                         }
                         if (p.c16 != nullptr) {
+                            if (lane == 0) mc_tma_store_wait_read();
+                            __syncwarp();
+                            // 64-byte rows, 16-byte pieces XOR-ed with bits 1-2 of the row number (the 64-byte swizzle)
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const int rr = q * 8 + (lane >> 2);
-                                const int cc = (lane & 3) * 2;
-                                const float4 lo = mc_ld_shared_v4(stage_base + rr * 128 + ((cc ^ (rr & 7)) << 4));
-                                const float4 hi = mc_ld_shared_v4(stage_base + rr * 128 + (((cc + 1) ^ (rr & 7)) << 4));
-                                uint4 pack;
-                                pack.x = mc_to_half2(lo.x, lo.y, p.c16_kind);
-                                pack.y = mc_to_half2(lo.z, lo.w, p.c16_kind);
-                                pack.z = mc_to_half2(hi.x, hi.y, p.c16_kind);
-                                pack.w = mc_to_half2(hi.z, hi.w, p.c16_kind);
-                                if (row_base + rr < p.m) {
-                                    *reinterpret_cast<uint4*>(p.c16 + (long long)(row_base + rr) * p.ldc16 + col0 + cc * 4) = pack;
-                                }
+                            for (int j = 0; j < 4; ++j) {
+                                mc_st_shared_v4u(stage_base + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4),
+                                                 mc_to_half2(f[8 * j + 0], f[8 * j + 1], p.c16_kind),
+                                                 mc_to_half2(f[8 * j + 2], f[8 * j + 3], p.c16_kind),
+                                                 mc_to_half2(f[8 * j + 4], f[8 * j + 5], p.c16_kind),
+                                                 mc_to_half2(f[8 * j + 6], f[8 * j + 7], p.c16_kind));
                             }
+                            mc_fence_async_shared();
+                            __syncwarp();
+                            if (lane == 0) mc_tma_store_2d(&map_c16, stage_base, col0, row_base);
                         }
-                        __syncwarp();
                     } else if (row < p.m) {
                         if (p.c != nullptr) {
                             float* out = p.c + (long long)row * p.ldc + col0;
@@ -468,6 +484,8 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
             }
             acc ^= 1;
         }
+        // Every store this warp issued has completed before the CTA gives up its shared memory.
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     __syncwarp();
@@ -482,48 +500,54 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
 
 #if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc2_h16_bmn)
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
-mc_gemm_tc2_h16_bmn(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
+mc_gemm_tc2_h16_bmn(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
+                    const __grid_constant__ McTensorMap map_c, const __grid_constant__ McTensorMap map_c16, const McTcParams p,
                     const McEpilogueArgs epi) {
-    mc_gemm_tc2_body<2, false, false>(map_a, map_b, p, epi);
+    mc_gemm_tc2_body<2, false, false>(map_a, map_b, map_c, map_c16, p, epi);
 }
 #endif
 
 #if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc2_h16_bk)
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
-mc_gemm_tc2_h16_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
+mc_gemm_tc2_h16_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
+                   const __grid_constant__ McTensorMap map_c, const __grid_constant__ McTensorMap map_c16, const McTcParams p,
                    const McEpilogueArgs epi) {
-    mc_gemm_tc2_body<2, true, false>(map_a, map_b, p, epi);
+    mc_gemm_tc2_body<2, true, false>(map_a, map_b, map_c, map_c16, p, epi);
 }
 #endif
 
 #if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc2_tf32_bk)
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
-mc_gemm_tc2_tf32_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
+mc_gemm_tc2_tf32_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
+                    const __grid_constant__ McTensorMap map_c, const __grid_constant__ McTensorMap map_c16, const McTcParams p,
                     const McEpilogueArgs epi) {
-    mc_gemm_tc2_body<4, true, false>(map_a, map_b, p, epi);
+    mc_gemm_tc2_body<4, true, false>(map_a, map_b, map_c, map_c16, p, epi);
 }
 #endif
 
 #if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc2w_h16_bmn)
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
-mc_gemm_tc2w_h16_bmn(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
+mc_gemm_tc2w_h16_bmn(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
+                     const __grid_constant__ McTensorMap map_c, const __grid_constant__ McTensorMap map_c16, const McTcParams p,
                      const McEpilogueArgs epi) {
-    mc_gemm_tc2_body<2, false, true>(map_a, map_b, p, epi);
+    mc_gemm_tc2_body<2, false, true>(map_a, map_b, map_c, map_c16, p, epi);
 }
 #endif
 
 #if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc2w_h16_bk)
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
-mc_gemm_tc2w_h16_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
+mc_gemm_tc2w_h16_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
+                    const __grid_constant__ McTensorMap map_c, const __grid_constant__ McTensorMap map_c16, const McTcParams p,
                     const McEpilogueArgs epi) {
-    mc_gemm_tc2_body<2, true, true>(map_a, map_b, p, epi);
+    mc_gemm_tc2_body<2, true, true>(map_a, map_b, map_c, map_c16, p, epi);
 }
 #endif
 
 #if !defined(MC_SINGLE_ENTRY) || defined(MC_ONLY_mc_gemm_tc2w_tf32_bk)
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MC_TC_THREADS, 1)
-mc_gemm_tc2w_tf32_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b, const McTcParams p,
+mc_gemm_tc2w_tf32_bk(const __grid_constant__ McTensorMap map_a, const __grid_constant__ McTensorMap map_b,
+                     const __grid_constant__ McTensorMap map_c, const __grid_constant__ McTensorMap map_c16, const McTcParams p,
                      const McEpilogueArgs epi) {
-    mc_gemm_tc2_body<4, true, true>(map_a, map_b, p, epi);
+    mc_gemm_tc2_body<4, true, true>(map_a, map_b, map_c, map_c16, p, epi);
 }
 #endif
