@@ -65,10 +65,18 @@ int split_k_splits(int m, int n, int k, int sm_count, int blocks_per_sm) {
     return static_cast<int>(std::max<std::int64_t>(splits, 1));
 }
 
-int tensor_core_tile_n(int m, int n, int k, int sm_count, int elem_bytes) {
+namespace {
+
+struct TensorCoreTiling {
+    int tile_n;
+    int splits;
+};
+
+TensorCoreTiling tensor_core_tiling(int m, int n, int k, int sm_count, int elem_bytes, bool narrow_single_row = true) {
     const std::int64_t rows = (static_cast<std::int64_t>(m) + 127) / 128;
     const std::int64_t sms = sm_count;
-    if (5 * rows * ((static_cast<std::int64_t>(n) + 255) / 256) >= 4 * sms) return 256;
+    const std::int64_t wide_tiles = rows * ((static_cast<std::int64_t>(n) + 255) / 256);
+    if (5 * wide_tiles >= 4 * sms) return {256, 1};
     // A problem too small to fill the SMs with 128 x 256 tiles: narrower tiles in one launch beat a K split plus
     // its reduction pass as long as the extra operand traffic stays small (every tile re-reads its 128 rows of A).
     const std::int64_t block_k = 128 / elem_bytes;
@@ -76,20 +84,33 @@ int tensor_core_tile_n(int m, int n, int k, int sm_count, int elem_bytes) {
     for (int width : {128, 64}) {
         const std::int64_t tiles = rows * ((static_cast<std::int64_t>(n) + width - 1) / width);
         const std::int64_t traffic = tiles * k_blocks * (128 * 128 + width * 128);
-        if (5 * tiles >= 4 * sms || width == 64) return traffic <= kNarrowTileTrafficLimit && 2 * tiles >= sms ? width : 256;
+        if (5 * tiles >= 4 * sms || width == 64) {
+            if (traffic <= kNarrowTileTrafficLimit && 2 * tiles >= sms) return {width, 1};
+            break;
+        }
     }
-    return 256;
+    // Split K, at least 4 K blocks per work item.
+    const std::int64_t wide_splits = std::max<std::int64_t>(1, std::min<std::int64_t>(sms / wide_tiles, k_blocks / 4));
+    // A single row of tiles (up to 128 rows of A) that would be cut 4 or more ways: 128-column tiles need half the K
+    // slices for the same number of work items, so half the partial sums are written and added up again, and with
+    // fewer than 128 rows the ring stages only the rows there are and is deep enough for the narrower B tiles
+    // (128 x 8192 x 8192: 40.0 against 44.0 us; 64 rows: 37.9 against 40.0; 16 and 32 rows: the same 38 us).
+    if (narrow_single_row && rows == 1 && wide_splits >= 4) {
+        const std::int64_t tiles = (static_cast<std::int64_t>(n) + 127) / 128;
+        const std::int64_t splits = std::max<std::int64_t>(1, std::min<std::int64_t>(sms / tiles, k_blocks / 4));
+        if (splits >= 2) return {128, static_cast<int>(splits)};
+    }
+    return {256, static_cast<int>(wide_splits)};
+}
+
+}  // namespace
+
+int tensor_core_tile_n(int m, int n, int k, int sm_count, int elem_bytes) {
+    return tensor_core_tiling(m, n, k, sm_count, elem_bytes).tile_n;
 }
 
 int tensor_core_splits(int m, int n, int k, int sm_count, int elem_bytes) {
-    const std::int64_t tiles = ((static_cast<std::int64_t>(m) + 127) / 128) * ((static_cast<std::int64_t>(n) + 255) / 256);
-    const std::int64_t sms = sm_count;
-    if (5 * tiles >= 4 * sms) return 1;
-    if (tensor_core_tile_n(m, n, k, sm_count, elem_bytes) != 256) return 1;
-    const std::int64_t block_k = 128 / elem_bytes;
-    const std::int64_t k_blocks = (k + block_k - 1) / block_k;
-    std::int64_t splits = std::min<std::int64_t>(sms / tiles, k_blocks / 4);  // at least 4 K blocks per work item
-    return static_cast<int>(std::max<std::int64_t>(splits, 1));
+    return tensor_core_tiling(m, n, k, sm_count, elem_bytes).splits;
 }
 
 int balanced_fp32_splits(int m, int n, int k, int sm_count) {
@@ -127,6 +148,13 @@ bool tensor_core_cluster_reduce(int k, int elem_bytes, int splits, int tile_n, i
     const int per = (k_blocks + asked - 1) / asked;
     const int effective = (k_blocks + per - 1) / per;
     return effective == 2 || effective == 4 || effective == 8;
+}
+
+bool tensor_core_finish_in_kernel(int m, int n, int splits, int tile_n, bool cluster_reduce, int gemm_variant) {
+    if (splits <= 1 || cluster_reduce || (gemm_variant & 4096) == 0) return false;
+    const std::int64_t width = tile_n == 0 ? 256 : tile_n;
+    const std::int64_t tiles = ((static_cast<std::int64_t>(m) + 127) / 128) * ((static_cast<std::int64_t>(n) + width - 1) / width);
+    return tiles <= kMaxTileCounters;
 }
 
 MatmulKernel resolve_matmul_kernel(MatmulKernel kernel, int m, int n, int k, int sm_count) {
@@ -482,7 +510,11 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
                                                            : Arith::F32;
         s.splits = balanced > 1 ? balanced : matmul_splits(kernel, s.m, s.n, s.k, sm_count);
         if (is_tensor_core(kernel)) {
-            s.tile_n = tensor_core_tile_n(s.m, s.n, s.k, sm_count, kernel == MatmulKernel::TensorCoreTf32 ? 4 : 2);
+            // The slices of a tile can only meet inside clusters (variant bit 64) with 256-column tiles.
+            const TensorCoreTiling tiling = tensor_core_tiling(s.m, s.n, s.k, sm_count, kernel == MatmulKernel::TensorCoreTf32 ? 4 : 2,
+                                                               (options.gemm_variant & 64) == 0);
+            s.tile_n = tiling.tile_n;
+            s.splits = tiling.splits;
         }
         // TF32 always takes the [n,k] copy of B: with 32-bit elements the MN-major shared-memory form did not
         // yield correct products on B200, while the K-major form does. 16-bit operands work in both forms.
@@ -491,6 +523,10 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
         if (is_tensor_core(kernel) && s.splits > 1 &&
             tensor_core_cluster_reduce(s.k, kernel == MatmulKernel::TensorCoreTf32 ? 4 : 2, s.splits, s.tile_n, options.gemm_variant)) {
             s.launches = 1;  // the K slices of a tile meet inside a thread-block cluster: no second launch, no workspace
+        } else if (is_tensor_core(kernel) &&
+                   tensor_core_finish_in_kernel(s.m, s.n, s.splits, s.tile_n, false, options.gemm_variant)) {
+            s.launches = 1;  // the last K slice of a tile to arrive adds the partial tiles: no second launch
+            s.finish_in_kernel = true;
         }
         return s;
     };
@@ -631,8 +667,13 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
     for (std::size_t i = 0; i < out.steps.size(); ++i) {
         const Step& s = out.steps[i];
         out.kernel_launches += static_cast<std::size_t>(s.launches) + out.after_step[i].size();
-        if (s.kind == Step::Kind::Matmul && s.splits > 1 && s.launches > 1) {
+        if (s.kind == Step::Kind::Matmul && s.splits > 1 && (s.launches > 1 || s.finish_in_kernel)) {
             out.workspace_bytes = std::max(out.workspace_bytes, static_cast<std::size_t>(s.splits) * s.m * s.n * sizeof(float));
+        }
+        if (s.kind == Step::Kind::Matmul && s.finish_in_kernel) {
+            const std::size_t tiles = (static_cast<std::size_t>(s.m) + 127) / 128 *
+                                      ((static_cast<std::size_t>(s.n) + s.tile_n - 1) / s.tile_n);
+            out.counter_words = std::max(out.counter_words, tiles);
         }
     }
 
@@ -807,6 +848,7 @@ std::string describe(const Graph& graph, const LoweredGraph& lowered) {
                << matmul_kernel_name(s.kernel) << " splits=" << s.splits;
             if (s.tile_n != 256) os << " tile_n=" << s.tile_n;
             if (s.rhs_transposed) os << " rhs=transposed";
+            if (s.finish_in_kernel) os << " finish=in_kernel";
             if (s.has_epilogue) os << " epilogue=" << graph.node(s.result).name << "(" << s.program.num_ops() << " ops)";
         }
         os << " out=" << (s.write_f32 ? "f32" : "") << (s.write_f32 && s.write_half != HalfKind::None ? "+" : "")

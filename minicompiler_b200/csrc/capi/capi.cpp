@@ -588,7 +588,7 @@ std::string step_source(const Graph& g, const cuda::CudaOptions& parsed, const c
             return cuda::generate_row_reduce_kernel(step.reduce_op, step.program, shapes, step.reduce_shape).source;
         case cuda::Step::Kind::Matmul:
             if (!step.has_epilogue) return {};
-            return cuda::generate_epilogue_source(g, step) + mcd_gemm_source(step.splits > 1 ? -1 : static_cast<int>(step.arith));
+            return cuda::generate_epilogue_source(g, step) + mcd_gemm_source(step.launches > 1 ? -1 : static_cast<int>(step.arith));
     }
     return {};
 }

@@ -444,10 +444,15 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
                                                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     McTensorMap map_a, map_b;
     static_assert(sizeof(McTensorMap) == sizeof(CUtensorMap), "tensor map size");
-    if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_a), type, elem, a->a, a->k, a->m, a->lda, block_k, MC_TC_BM)) {
+    const bool pairs = tc_uses_pairs(a);
+    // The one-CTA kernel stages only the rows a problem of fewer than 128 rows has (in whole groups of 8), and cuts
+    // its ring out of the same shared memory: as many stages as fit, leaving room behind the last one for the 128
+    // rows an MMA reads from wherever its A tile starts.
+    const int a_rows = (!pairs && a->m < MC_TC_BM) ? (a->m + 7) / 8 * 8 : MC_TC_BM;
+    if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_a), type, elem, a->a, a->k, a->m, a->lda, block_k,
+                            static_cast<unsigned>(a_rows))) {
         return rc;
     }
-    const bool pairs = tc_uses_pairs(a);
     if (b_k_major) {
         // A CTA of the pair kernel keeps 128 of the tile's 256 columns.
         if (int rc = encode_map(reinterpret_cast<CUtensorMap*>(&map_b), type, elem, a->b, a->k, a->n, a->ldb, block_k,
@@ -479,6 +484,13 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     p.wide = 0;
     p.cluster_reduce = cluster ? splits : 0;
     p.staged = (a->variant & 128) == 0 ? 1 : 0;
+    p.a_rows = a_rows;
+    p.tile_counters = (splits > 1 && !cluster) ? a->tile_counters : nullptr;
+    {
+        const int stage_bytes = (a_rows + tile_n) * 128;
+        const int room = MC_TC_STAGES * MC_TC_STAGE_BYTES - (MC_TC_BM - a_rows) * 128;
+        p.stages = std::max(2, std::min(MC_TC_MAX_STAGES, room / stage_bytes));
+    }
     // Tiles that do not fill the last wave of CTAs are cut in two when both halves of all of them fit in one wave.
     const int sms = sm_count_of_current_device();
     const int all_tiles = ((a->m + MC_TC_BM - 1) / MC_TC_BM) * ((a->n + tile_n - 1) / tile_n);
@@ -555,7 +567,7 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
         return mcd_launch_cluster(a->function, static_cast<unsigned>(tiles), static_cast<unsigned>(splits), MC_TC_THREADS,
                                   MC_TC_SMEM_BYTES, s, params);
     }
-    if (a->function != nullptr && splits == 1) {
+    if (a->function != nullptr && (splits == 1 || p.tile_counters != nullptr)) {
         void* params[] = {&map_a, &map_b, &p, &epi};
         return mcd_launch(a->function, grid, 1, 1, MC_TC_THREADS, MC_TC_SMEM_BYTES, s, params);
     }
@@ -591,7 +603,7 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     }
     kernel<<<grid, MC_TC_THREADS, MC_TC_SMEM_BYTES, s>>>(map_a, map_b, p, epi);
     if (int rc = launched("mc_gemm_tc")) return rc;
-    if (splits > 1) return reduce_splits(a, splits, s);
+    if (splits > 1 && p.tile_counters == nullptr) return reduce_splits(a, splits, s);
     return 0;
 }
 
@@ -619,7 +631,7 @@ extern "C" int mcd_gemm_launches(const mcd_gemm_args* a) {
         int k_per_split = 0;
         return f32_splits(a, &k_per_split) > 1 ? 2 : 1;
     }
-    if (tc_cluster_reduce(a)) return 1;
+    if (tc_cluster_reduce(a) || a->tile_counters != nullptr) return 1;
     return tc_splits(a) > 1 ? 2 : 1;
 }
 
