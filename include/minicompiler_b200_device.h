@@ -211,11 +211,6 @@ typedef struct mcd_gemm_args {
                              for small unsplit problems (one-CTA kernel) */
     int has_epilogue;     /* non-zero when the launch carries a generated epilogue; set it before asking for the
                              entry point as well, kernel selection depends on it */
-    unsigned int* tile_counters; /* tensor-core arithmetic with splits > 1: NULL, or device words, one per 128 x tile_n
-                             tile of C, zero before the first launch. The K slices of a tile then count themselves in as
-                             they finish, and the slice that arrives last adds the partial tiles in slice order, applies
-                             the epilogue and writes C: one launch instead of two, the same sum in the same order. The
-                             kernel leaves every word zero again. Ignored when the slices meet inside clusters. */
 } mcd_gemm_args;
 
 MCD_API int mcd_gemm(const mcd_gemm_args* args, void* stream);

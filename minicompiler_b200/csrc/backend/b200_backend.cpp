@@ -509,8 +509,7 @@ private:
         MCD_TRY(mcd_copy_d2h(&word, status_word(), sizeof word, stream_));
         MCD_TRY(mcd_stream_synchronize(stream_));
         if (word != 0) {
-            // A kernel that gave up may have left tile counters half-way: the whole region starts over.
-            MCD_TRY(mcd_memset(status_word(), 0, status_region_bytes_, stream_));
+            MCD_TRY(mcd_memset(status_word(), 0, sizeof word, stream_));
             return Error{"a matmul kernel gave up a bounded wait (status 0x" + to_hex(word) +
                          "): results of this run are incomplete"};
         }
@@ -524,7 +523,6 @@ private:
     }
 
     unsigned* status_word() const { return reinterpret_cast<unsigned*>(static_cast<char*>(arena_) + status_offset_); }
-    unsigned* tile_counters() const { return status_word() + kAlign / sizeof(unsigned); }
 
     Status issue(const Launch& l, void* stream) const {
         switch (l.kind) {
@@ -648,15 +646,11 @@ private:
         const std::size_t workspace_bytes = std::max(lowered_.workspace_bytes, slice_rows_ > 0 ? slice_lowered_.workspace_bytes : 0);
         const std::size_t workspace_offset = cursor;
         cursor += align_up(workspace_bytes);
-        // The status word, then the tile counters of the matmuls that finish split tiles in the kernel: zero here, and
-        // left zero by every launch that completes.
         status_offset_ = cursor;
-        status_region_bytes_ = kAlign + align_up(std::max(lowered_.counter_words, slice_rows_ > 0 ? slice_lowered_.counter_words : 0) *
-                                                 sizeof(unsigned));
-        cursor += status_region_bytes_;
+        cursor += kAlign;
         arena_bytes_ = cursor;
         MCD_TRY(mcd_malloc(&arena_, arena_bytes_));
-        MCD_TRY(mcd_memset(status_word(), 0, status_region_bytes_, stream_));
+        MCD_TRY(mcd_memset(status_word(), 0, kAlign, stream_));
         float* workspace = workspace_bytes > 0 ? reinterpret_cast<float*>(static_cast<char*>(arena_) + workspace_offset) : nullptr;
 
         // ---- constants: uploaded once, derived forms made once
@@ -797,7 +791,6 @@ private:
             if (mine.kind == Step::Kind::Matmul) {
                 mine.splits = full.splits;
                 mine.launches = full.launches;
-                mine.finish_in_kernel = full.finish_in_kernel;
                 if (mine.splits > 1) {
                     lowered->workspace_bytes = std::max(
                         lowered->workspace_bytes, static_cast<std::size_t>(mine.splits) * mine.m * mine.n * sizeof(float));
@@ -993,7 +986,6 @@ private:
         g.splits = step.splits;
         g.tile_n = step.tile_n;
         g.workspace = step.splits > 1 ? workspace : nullptr;
-        g.tile_counters = step.finish_in_kernel ? tile_counters() : nullptr;
         g.variant = options_.gemm_variant;
         // Kernels fed by TMA wait on mbarriers; a wait that gives up reports through this word.
         g.status = status_word();
@@ -1061,7 +1053,6 @@ private:
     std::size_t arena_bytes_ = 0;
     std::size_t constants_bytes_ = 0;
     std::size_t status_offset_ = 0;
-    std::size_t status_region_bytes_ = kAlign;
     bool uses_status_ = false;
     std::vector<std::size_t> offset_;  // per (node, rep): byte offset in the arena
     LaunchList launches_;

@@ -150,13 +150,6 @@ bool tensor_core_cluster_reduce(int k, int elem_bytes, int splits, int tile_n, i
     return effective == 2 || effective == 4 || effective == 8;
 }
 
-bool tensor_core_finish_in_kernel(int m, int n, int splits, int tile_n, bool cluster_reduce, int gemm_variant) {
-    if (splits <= 1 || cluster_reduce || (gemm_variant & 4096) == 0) return false;
-    const std::int64_t width = tile_n == 0 ? 256 : tile_n;
-    const std::int64_t tiles = ((static_cast<std::int64_t>(m) + 127) / 128) * ((static_cast<std::int64_t>(n) + width - 1) / width);
-    return tiles <= kMaxTileCounters;
-}
-
 MatmulKernel resolve_matmul_kernel(MatmulKernel kernel, int m, int n, int k, int sm_count) {
     if (kernel != MatmulKernel::Auto) return kernel;
     return split_k_splits(m, n, k, sm_count) > 1 ? MatmulKernel::SplitK : MatmulKernel::DoubleBuffered;
@@ -523,10 +516,6 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
         if (is_tensor_core(kernel) && s.splits > 1 &&
             tensor_core_cluster_reduce(s.k, kernel == MatmulKernel::TensorCoreTf32 ? 4 : 2, s.splits, s.tile_n, options.gemm_variant)) {
             s.launches = 1;  // the K slices of a tile meet inside a thread-block cluster: no second launch, no workspace
-        } else if (is_tensor_core(kernel) &&
-                   tensor_core_finish_in_kernel(s.m, s.n, s.splits, s.tile_n, false, options.gemm_variant)) {
-            s.launches = 1;  // the last K slice of a tile to arrive adds the partial tiles: no second launch
-            s.finish_in_kernel = true;
         }
         return s;
     };
@@ -667,13 +656,8 @@ Result<LoweredGraph> lower_graph(const Graph& graph, const CudaOptions& options,
     for (std::size_t i = 0; i < out.steps.size(); ++i) {
         const Step& s = out.steps[i];
         out.kernel_launches += static_cast<std::size_t>(s.launches) + out.after_step[i].size();
-        if (s.kind == Step::Kind::Matmul && s.splits > 1 && (s.launches > 1 || s.finish_in_kernel)) {
+        if (s.kind == Step::Kind::Matmul && s.splits > 1 && s.launches > 1) {
             out.workspace_bytes = std::max(out.workspace_bytes, static_cast<std::size_t>(s.splits) * s.m * s.n * sizeof(float));
-        }
-        if (s.kind == Step::Kind::Matmul && s.finish_in_kernel) {
-            const std::size_t tiles = (static_cast<std::size_t>(s.m) + 127) / 128 *
-                                      ((static_cast<std::size_t>(s.n) + s.tile_n - 1) / s.tile_n);
-            out.counter_words = std::max(out.counter_words, tiles);
         }
     }
 
@@ -848,7 +832,6 @@ std::string describe(const Graph& graph, const LoweredGraph& lowered) {
                << matmul_kernel_name(s.kernel) << " splits=" << s.splits;
             if (s.tile_n != 256) os << " tile_n=" << s.tile_n;
             if (s.rhs_transposed) os << " rhs=transposed";
-            if (s.finish_in_kernel) os << " finish=in_kernel";
             if (s.has_epilogue) os << " epilogue=" << graph.node(s.result).name << "(" << s.program.num_ops() << " ops)";
         }
         os << " out=" << (s.write_f32 ? "f32" : "") << (s.write_f32 && s.write_half != HalfKind::None ? "+" : "")

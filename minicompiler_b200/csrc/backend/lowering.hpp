@@ -62,14 +62,6 @@ int tensor_core_tile_n(int m, int n, int k, int sm_count, int elem_bytes);
 // default: it measured no faster than the second launch it saves). The device layer
 // applies the same rule when it launches (tc_cluster_reduce in gemm_launch.cu; a host test compares the two).
 bool tensor_core_cluster_reduce(int k, int elem_bytes, int splits, int tile_n, int gemm_variant);
-// Whether a tensor-core matmul split `splits` ways lets the last-arriving K slice of each tile finish the tile (one
-// launch) instead of running the reduction kernel afterwards: asked for with gemm_variant bit 4096, when the slices
-// do not meet inside clusters and the tiles fit the counter region. Off by default: the chain of device-wide fence,
-// counter update and re-read of the partial tiles by one CTA per tile measured slower than the reduction kernel, which
-// is launched as a programmatic dependent and spreads over every SM (16 x 8192 x 8192: 41.0 against 37.9 us;
-// 128 x 8192 x 8192: 65.6 against 44.0 us; 1024 x 1024 x 65536: 139 against 116 us). Tiles = 128-row x tile_n blocks.
-constexpr std::int64_t kMaxTileCounters = 4096;
-bool tensor_core_finish_in_kernel(int m, int n, int splits, int tile_n, bool cluster_reduce, int gemm_variant);
 MatmulKernel resolve_matmul_kernel(MatmulKernel kernel, int m, int n, int k, int sm_count);
 int matmul_splits(MatmulKernel kernel, int m, int n, int k, int sm_count);
 std::size_t matmul_workspace_bytes(MatmulKernel kernel, int m, int n, int splits);
@@ -157,9 +149,6 @@ struct Step {
     bool write_f32 = true;
     HalfKind write_half = HalfKind::None;
     int launches = 1;
-    // A split tensor-core matmul whose last-arriving K slice adds the partial tiles itself (one launch; the
-    // workspace is still used, plus one counter word per tile).
-    bool finish_in_kernel = false;
 };
 
 // A copy made right after a step (or right after upload, for inputs): f32 -> another Rep.
@@ -183,7 +172,6 @@ struct LoweredGraph {
     std::vector<PoolStep> pool_steps;
     PoolPlan pool;
     std::size_t workspace_bytes = 0;  // one split-K workspace shared by all steps
-    std::size_t counter_words = 0;    // tile counters of the matmuls that finish split tiles in the kernel (shared likewise)
 };
 
 // Row pitch (in elements) of the 16-bit copy of a rank-2 tensor with `cols` columns:

@@ -485,7 +485,6 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     p.cluster_reduce = cluster ? splits : 0;
     p.staged = (a->variant & 128) == 0 ? 1 : 0;
     p.a_rows = a_rows;
-    p.tile_counters = (splits > 1 && !cluster) ? a->tile_counters : nullptr;
     {
         const int stage_bytes = (a_rows + tile_n) * 128;
         const int room = MC_TC_STAGES * MC_TC_STAGE_BYTES - (MC_TC_BM - a_rows) * 128;
@@ -567,7 +566,7 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
         return mcd_launch_cluster(a->function, static_cast<unsigned>(tiles), static_cast<unsigned>(splits), MC_TC_THREADS,
                                   MC_TC_SMEM_BYTES, s, params);
     }
-    if (a->function != nullptr && (splits == 1 || p.tile_counters != nullptr)) {
+    if (a->function != nullptr && splits == 1) {
         void* params[] = {&map_a, &map_b, &p, &epi};
         return mcd_launch(a->function, grid, 1, 1, MC_TC_THREADS, MC_TC_SMEM_BYTES, s, params);
     }
@@ -603,7 +602,7 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
     }
     kernel<<<grid, MC_TC_THREADS, MC_TC_SMEM_BYTES, s>>>(map_a, map_b, p, epi);
     if (int rc = launched("mc_gemm_tc")) return rc;
-    if (splits > 1 && p.tile_counters == nullptr) return reduce_splits(a, splits, s);
+    if (splits > 1) return reduce_splits(a, splits, s);
     return 0;
 }
 
@@ -631,7 +630,7 @@ extern "C" int mcd_gemm_launches(const mcd_gemm_args* a) {
         int k_per_split = 0;
         return f32_splits(a, &k_per_split) > 1 ? 2 : 1;
     }
-    if (tc_cluster_reduce(a) || a->tile_counters != nullptr) return 1;
+    if (tc_cluster_reduce(a)) return 1;
     return tc_splits(a) > 1 ? 2 : 1;
 }
 

@@ -71,10 +71,6 @@ struct McTcParams {
                      // problem fill the SMs in one launch instead of splitting K (idesc carries the same N)
     int cluster_reduce;  // one-CTA kernel only: 0, or the K splits of a tile are the CTAs of a cluster of this size,
                          // which add their partial tiles through distributed shared memory (one work item per CTA)
-    unsigned* tile_counters;  // one-CTA kernel, splits > 1: null, or one zero-initialised word per tile. The K slices of a
-                              // tile then count themselves in as they finish; the slice that arrives last adds all the
-                              // partial tiles in slice order, applies the epilogue and writes C (one launch instead of
-                              // two; the sum and its order are those of mc_splitk_reduce), and re-arms the word.
     int stages;  // one-CTA kernel only: depth of the operand ring, 2 .. MC_TC_MAX_STAGES
     int a_rows;  // one-CTA kernel only: rows of A staged per K block (the box of A's tensor map), a multiple of 8 up to 128.
                  // A problem of fewer than 128 rows stages only its own rows: a stage shrinks to a_rows * 128 bytes of A
@@ -254,9 +250,6 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
     // of every CTA has delivered its partial sums)
     const unsigned bar_peers_done = bar_tmem_empty + 16;
     const unsigned bar_data_ready = bar_peers_done + 8;
-    // in-kernel finish of a split tile: the epilogue warps meet here before and after the tile's count is taken
-    const unsigned bar_epilogue_meet = bar_data_ready + 8;
-    __shared__ int last_slice_flag;
     __shared__ unsigned tmem_base_slot;
     __shared__ int abort_flag_storage;
     volatile int* abort_flag = &abort_flag_storage;
@@ -266,7 +259,7 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
     // When K is split, the reduction kernel that follows is launched as a programmatic dependent: once every CTA of
     // this grid has passed this point its blocks may take their places (they wait for this grid to complete before
     // they read anything), which hides its launch latency behind the main loop.
-    if (p.splits > 1 && p.tile_counters == nullptr) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (p.splits > 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const int tiles_m = (p.m + MC_TC_BM - 1) / MC_TC_BM;
     const int bn = p.tile_n;  // columns per tile; accumulators stay MC_TC_BN TMEM columns apart
@@ -284,7 +277,6 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
             mc_mbar_init(bar_tmem_full + 8 * a, 1);
             mc_mbar_init(bar_tmem_empty + 8 * a, MC_TC_EPILOGUE_WARPS);  // one arrival per epilogue warp
         }
-        mc_mbar_init(bar_epilogue_meet, MC_TC_EPILOGUE_WARPS);
         if (p.cluster_reduce > 1) {
             mc_mbar_init(bar_peers_done, (unsigned)p.cluster_reduce);
             mc_mbar_init(bar_data_ready, (unsigned)(p.cluster_reduce * MC_TC_EPILOGUE_WARPS));
@@ -422,7 +414,6 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
         const int col_begin = ((warp - 2) >> 2) * kColsPerWarp;
         int acc = 0;
         unsigned acc_phase = 0;
-        unsigned meet_phase = 0;
         bool ok = true;
         const bool partial = p.splits > 1;
         if (p.cluster_reduce > 1) {
@@ -583,78 +574,6 @@ __device__ __forceinline__ void mc_gemm_tc_body(const McTensorMap& map_a, const 
             if (lane == 0) mc_mbar_arrive(bar_tmem_empty + 8 * acc);
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
-            if (partial && p.tile_counters != nullptr) {
-                // This slice's partial tile is in the workspace. Every thread makes its part visible device-wide, the
-                // warps meet, one thread counts the slice in; whoever completes the count knows that all the slices of
-                // the tile are visible and finishes the tile. Nobody waits for another CTA.
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) mc_mbar_arrive(bar_epilogue_meet);
-                ok = mc_mbar_wait(bar_epilogue_meet, meet_phase, abort_flag, p.status, MC_TC_ERR_EPILOGUE);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                meet_phase ^= 1u;
-                const int tile_id = mb * tiles_n + nb;
-                if (warp == 2 && lane == 0) {
-                    const unsigned before = atomicAdd(p.tile_counters + tile_id, 1u);
-                    const int last = before == (unsigned)(p.splits - 1) ? 1 : 0;
-                    if (last) p.tile_counters[tile_id] = 0u;  // nobody else touches it again in this launch
-                    last_slice_flag = last;
-                }
-                __syncwarp();
-                if (lane == 0) mc_mbar_arrive(bar_epilogue_meet);
-                ok = mc_mbar_wait(bar_epilogue_meet, meet_phase, abort_flag, p.status, MC_TC_ERR_EPILOGUE);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                meet_phase ^= 1u;
-                if (last_slice_flag != 0) {
-                    __threadfence();
-                    // Rows go round the 8 warps, lanes along the columns, so a problem of 16 rows still uses every warp;
-                    // all the slices of a group of 4 columns are requested together, then added in slice order.
-                    const long long slice = (long long)p.m * p.n;
-                    const int rows_here = min(MC_TC_BM, p.m - mb * MC_TC_BM);
-                    const int cols_here = min(bn, p.n - n0);
-                    const bool vec_ws = (p.n & 3) == 0 && (((unsigned long long)p.workspace) & 15) == 0;
-                    const bool vec_c = p.c == nullptr || ((p.ldc & 3) == 0 && (((unsigned long long)p.c) & 15) == 0);
-                    for (int r = warp - 2; r < rows_here; r += MC_TC_EPILOGUE_WARPS) {
-                        const int grow = mb * MC_TC_BM + r;
-                        const float* src = p.workspace + (long long)grow * p.n + n0;
-                        if (vec_ws && vec_c && (cols_here & 3) == 0) {
-                            for (int c = lane * 4; c < cols_here; c += 128) {
-                                float4 sum = __ldcg(reinterpret_cast<const float4*>(src + c));
-                                for (int z = 1; z < p.splits; ++z) {
-                                    const float4 part = __ldcg(reinterpret_cast<const float4*>(src + z * slice + c));
-                                    sum.x += part.x;
-                                    sum.y += part.y;
-                                    sum.z += part.z;
-                                    sum.w += part.w;
-                                }
-                                const unsigned gcol = (unsigned)(n0 + c);
-                                sum.x = mc_epilogue(sum.x, (unsigned)grow, gcol + 0, epi);
-                                sum.y = mc_epilogue(sum.y, (unsigned)grow, gcol + 1, epi);
-                                sum.z = mc_epilogue(sum.z, (unsigned)grow, gcol + 2, epi);
-                                sum.w = mc_epilogue(sum.w, (unsigned)grow, gcol + 3, epi);
-                                if (p.c != nullptr) *reinterpret_cast<float4*>(p.c + (long long)grow * p.ldc + gcol) = sum;
-                                if (p.c16 != nullptr) {
-                                    unsigned short* out16 = p.c16 + (long long)grow * p.ldc16 + gcol;
-                                    out16[0] = mc_to_half(sum.x, p.c16_kind);
-                                    out16[1] = mc_to_half(sum.y, p.c16_kind);
-                                    out16[2] = mc_to_half(sum.z, p.c16_kind);
-                                    out16[3] = mc_to_half(sum.w, p.c16_kind);
-                                }
-                            }
-                        } else {
-                            for (int c = lane; c < cols_here; c += 32) {
-                                float sum = __ldcg(src + c);
-                                for (int z = 1; z < p.splits; ++z) sum += __ldcg(src + z * slice + c);
-                                sum = mc_epilogue(sum, (unsigned)grow, (unsigned)(n0 + c), epi);
-                                if (p.c != nullptr) p.c[(long long)grow * p.ldc + n0 + c] = sum;
-                                if (p.c16 != nullptr) p.c16[(long long)grow * p.ldc16 + n0 + c] = mc_to_half(sum, p.c16_kind);
-                            }
-                        }
-                    }
-                }
-            }
         }
     }
 

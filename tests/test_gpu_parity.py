@@ -211,10 +211,8 @@ def _torch():
     return torch
 
 
-def _device_gemm(mc, arith, a, b, splits, b_transposed=False, half=None, variant=0, tile_n=0, counters=False, repeat=1):
-    """Calls mcd_gemm directly with device buffers held by torch; C is pre-filled with NaN. `counters`: hand over
-    zeroed tile counters (a split tensor-core matmul then finishes its tiles in the kernel) and check that the call
-    leaves them zero; `repeat`: launches of the same call, C re-filled with NaN before each."""
+def _device_gemm(mc, arith, a, b, splits, b_transposed=False, half=None, variant=0, tile_n=0):
+    """Calls mcd_gemm directly with device buffers held by torch; C is pre-filled with NaN."""
     torch = _torch()
     lib = mc.lib()
 
@@ -224,8 +222,7 @@ def _device_gemm(mc, arith, a, b, splits, b_transposed=False, half=None, variant
                     ("ldc", C.c_longlong), ("c16", C.c_void_p), ("c16_kind", C.c_int), ("ldc16", C.c_longlong),
                     ("splits", C.c_int), ("workspace", C.c_void_p), ("function", C.c_void_p), ("reduce_function", C.c_void_p),
                     ("epilogue_inputs", C.c_void_p * 6), ("num_epilogue_inputs", C.c_int), ("status", C.c_void_p),
-                    ("variant", C.c_int), ("tile_n", C.c_int), ("has_epilogue", C.c_int),
-                    ("tile_counters", C.c_void_p)]
+                    ("variant", C.c_int), ("tile_n", C.c_int), ("has_epilogue", C.c_int)]
 
     m, k = a.shape
     n = b.shape[1]
@@ -263,22 +260,13 @@ def _device_gemm(mc, arith, a, b, splits, b_transposed=False, half=None, variant
     args.status = status.data_ptr()
     args.variant = variant
     args.tile_n = tile_n
-    tile_counters = torch.zeros(4096, dtype=torch.int32, device=dev)
-    if counters:
-        args.tile_counters = tile_counters.data_ptr()
     lib.mcd_gemm.restype = C.c_int
-    lib.mcd_gemm_launches.restype = C.c_int
     lib.mcd_last_error.restype = C.c_char_p
     stream = torch.cuda.current_stream().cuda_stream
-    for _ in range(repeat):
-        tc.fill_(float("nan"))
-        rc = lib.mcd_gemm(C.byref(args), C.c_void_p(stream))
-        assert rc == 0, lib.mcd_last_error().decode()
+    rc = lib.mcd_gemm(C.byref(args), C.c_void_p(stream))
+    assert rc == 0, lib.mcd_last_error().decode()
     torch.cuda.synchronize()
     assert int(status[0].item()) == 0, f"kernel gave up a wait: status {int(status[0].item()):#x}"
-    assert int(tile_counters.abs().sum().item()) == 0, "tile counters were not left at zero"
-    if counters and arith != 0:
-        assert lib.mcd_gemm_launches(C.byref(args)) == 1
     return tc.cpu().numpy()
 
 
@@ -356,33 +344,6 @@ def test_tensor_core_cluster_reduction_direct(mc, oracle, name, arith, half, u, 
 
 @pytest.mark.parametrize("layout", [False, True])
 @pytest.mark.parametrize("name,arith,half,u,sub", TC_KINDS)
-def test_tensor_core_split_tiles_finished_in_the_kernel_direct(mc, oracle, name, arith, half, u, sub, layout):
-    """K split with tile counters handed over: every K slice writes its partial tile to the workspace and counts itself
-    in, the slice that arrives last adds the partial tiles in slice order and writes C (one launch). The bits are those
-    of the workspace-and-reduction-kernel form; the counters are zero again afterwards, so a second and third launch
-    of the same call give the same result. Ragged M, N and K, fewer rows than a tile (the ring then stages only those
-    rows), several tiles per CTA, narrow tiles."""
-    if half is None and not layout:
-        pytest.skip("TF32 reads B as a [n,k] copy only")
-    for m, k, n, tile_n in [(128, 512, 256, 0), (16, 2048, 512, 0), (300, 1004, 36, 0), (33, 264, 72, 0), (130, 4096, 1000, 0),
-                            (8, 4096, 2048, 128), (100, 2048, 1024, 64), (1024, 2048, 4096, 0), (20, 640, 8200, 128)]:
-        if half is None and (k % 4 or n % 4):
-            continue
-        a = oracle.uniform_values(m * k, 1, -1, 1).reshape(m, k)
-        b = oracle.uniform_values(k * n, 2, -1, 1).reshape(k, n)
-        exact, abs_dot = exact_and_abs(a, b)
-        for splits in [2, 3, 5]:
-            if (k + (31 if half is None else 63)) // (32 if half is None else 64) < splits:
-                continue
-            in_kernel = _device_gemm(mc, arith, a, b, splits, b_transposed=layout, half=half, tile_n=tile_n, counters=True, repeat=3)
-            separate = _device_gemm(mc, arith, a, b, splits, b_transposed=layout, half=half, tile_n=tile_n)
-            what = f"{name} {m}x{k}x{n} tile_n={tile_n} splits={splits} transposed={layout}"
-            assert np.array_equal(in_kernel, separate), what
-            check_bound(in_kernel, exact, abs_dot, k, u, sub, what)
-
-
-@pytest.mark.parametrize("layout", [False, True])
-@pytest.mark.parametrize("name,arith,half,u,sub", TC_KINDS)
 def test_tensor_core_narrow_tiles_direct(mc, oracle, name, arith, half, u, sub, layout):
     """128 x 128 and 128 x 64 tiles of the one-CTA kernel give the bits of its 128 x 256 tiles."""
     if half is None and not layout:
@@ -436,23 +397,6 @@ def test_tensor_core_matmuls_within_their_precision_bounds(mc, oracle, name, ari
                 got = exe.run(ins)[0]
                 kernels = exe.matmul_kernels
             check_bound(got, exact, abs_dot, k, u, sub, f"{name} {m}x{k}x{n} {layout} ran {kernels}")
-
-
-def test_split_matmul_with_epilogue_finished_in_the_kernel_through_the_backend(mc, oracle):
-    """gemm_variant bit 4096 through a compiled graph: a skinny matmul whose K is split, with a bias and relu folded into
-    it, finishes its tiles in the matmul kernel (one launch; the epilogue is compiled into that kernel) and gives the
-    bits of the default two-launch form, run after run (the tile counters in the arena are left at zero)."""
-    text = ("dim M = 24\ndim K = 4096\ndim N = 2048\ninput x : f32[M, K]\nconst w : f32[K, N] = uniform(seed=5, lo=-0.05, hi=0.05)\n"
-            "const b : f32[N] = uniform(seed=6, lo=-0.5, hi=0.5)\nh = matmul x, w\nhb = add h, b\ny = relu hb\noutput y")
-    g, ins = oracle_inputs(oracle, text, seed=4)
-    for name in ["tensor_core_bf16", "tensor_core_tf32"]:
-        with mc.CompiledGraph(text=text, options={"matmul": name}) as exe:
-            separate = exe.run(ins)[0]
-            assert exe.kernel_launches == 2
-        with mc.CompiledGraph(text=text, options={"matmul": name, "gemm_variant": 4096}) as exe:
-            assert exe.kernel_launches == 1
-            for _ in range(3):
-                assert np.array_equal(exe.run(ins)[0], separate), name
 
 
 # -------------------------------------------------- the benchmark configs, small

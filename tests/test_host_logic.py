@@ -641,13 +641,10 @@ def test_row_slicing_analysis(mc):
     assert "y = fused %7, %4, %0 : f32[128,128]  (output)" in sliced
 
 
-def test_split_tensor_core_matmuls_take_one_launch(mc):
-    """A tensor-core matmul whose K is split adds its partial tiles in a reduction kernel launched behind it (two
-    launches, a workspace). Two one-launch forms can be asked for: with gemm_variant bit 4096 the K slice of a tile that
-    arrives last adds the partial tiles (workspace plus one counter word per tile); with bit 64 and 2, 4 or 8 slices
-    the slices meet inside thread-block clusters (no workspace). The lowering (which counts launches and sizes the
-    workspace) and the device layer (which launches) each apply these rules; they must agree for every shape and
-    split count."""
+def test_split_tensor_core_matmuls_that_reduce_in_a_cluster_need_one_launch_and_no_workspace(mc):
+    """With gemm_variant bit 64 a tensor-core matmul whose K is split 2, 4 or 8 ways adds its partial tiles inside
+    thread-block clusters: one launch, no workspace. The lowering (which counts launches and sizes the workspace) and the device layer (which
+    launches) each apply the rule; they must agree for every shape and split count."""
     lib = mc.lib()
 
     class GemmArgs(ctypes.Structure):
@@ -657,41 +654,31 @@ def test_split_tensor_core_matmuls_take_one_launch(mc):
                     ("ldc16", ctypes.c_longlong), ("splits", ctypes.c_int), ("workspace", ctypes.c_void_p),
                     ("function", ctypes.c_void_p), ("reduce_function", ctypes.c_void_p), ("epilogue_inputs", ctypes.c_void_p * 6),
                     ("num_epilogue_inputs", ctypes.c_int), ("status", ctypes.c_void_p), ("variant", ctypes.c_int),
-                    ("tile_n", ctypes.c_int), ("has_epilogue", ctypes.c_int),
-                    ("tile_counters", ctypes.c_void_p)]
+                    ("tile_n", ctypes.c_int), ("has_epilogue", ctypes.c_int)]
 
     lib.mcd_gemm_launches.restype = ctypes.c_int
     text = "dim M = 8\ndim N = 8\ndim K = 8\ninput a : f32[M, K]\ninput b : f32[K, N]\nc = matmul a, b\noutput c"
     for m, n, k in [(128, 8192, 8192), (16, 8192, 8192), (1024, 1024, 65536), (256, 2048, 512), (128, 256, 100000), (384, 1024, 4096),
                     (640, 1280, 2048), (128, 4096, 520), (4096, 4096, 4096)]:
         for name, arith, elem in (("tensor_core_bf16", 2, 2), ("tensor_core_tf32", 1, 4)):
-            for variant in (0, 64, 4096, 64 + 4096):
+            for variant in (0, 64):
                 plan = mc.HostGraph(text=text, dims={"M": m, "N": n, "K": k}).launch_plan({"matmul": name, "gemm_variant": variant})
                 splits = int(re.search(r"splits=(\d+)", plan).group(1))
                 launches = int(re.search(r"launches=(\d+)\n", plan).group(1))
                 workspace = int(re.search(r"workspace_bytes=(\d+)", plan).group(1))
                 tile_n = int(m_.group(1)) if (m_ := re.search(r"tile_n=(\d+)", plan)) else 0
-                in_kernel = "finish=in_kernel" in plan
-                # the caller hands over counters exactly where the plan says the kernel finishes the tiles itself
-                args = GemmArgs(arith=arith, m=m, n=n, k=k, splits=splits, variant=variant, tile_n=tile_n,
-                                tile_counters=ctypes.c_void_p(256) if in_kernel else None)
+                args = GemmArgs(arith=arith, m=m, n=n, k=k, splits=splits, variant=variant, tile_n=tile_n)
                 assert lib.mcd_gemm_launches(ctypes.byref(args)) == launches, (m, n, k, name, variant, plan)
-                assert (workspace > 0) == (launches == 2 or in_kernel), plan
-                if splits == 1:
-                    assert launches == 1 and not in_kernel
-                elif variant == 0:
-                    assert launches == 2 and not in_kernel, plan
-                elif variant == 4096:
-                    assert launches == 1 and in_kernel, plan
-    # the config shapes: skinny and tall-K problems split 4 ways
+                assert (workspace > 0) == (launches == 2), plan
+                if variant == 0:
+                    assert launches == (2 if splits > 1 else 1)
+    # the config shapes. Clusters asked for: 256-column tiles split 4 ways, one launch, no workspace. Default: the skinny
+    # problems take 128-column tiles and 2 K slices, the tall-K one 256-column tiles and 4; two launches each.
     for m, n, k in [(128, 8192, 8192), (16, 8192, 8192), (1024, 1024, 65536)]:
         plan = mc.HostGraph(text=text, dims={"M": m, "N": n, "K": k}).launch_plan({"matmul": "tensor_core_bf16", "gemm_variant": 64})
-        assert "splits=4" in plan and "launches=1\n" in plan and "workspace_bytes=0" in plan and "finish=in_kernel" not in plan, plan
-        splits = "splits=4" if m > 128 else "splits=2 tile_n=128"
-        plan = mc.HostGraph(text=text, dims={"M": m, "N": n, "K": k}).launch_plan({"matmul": "tensor_core_bf16", "gemm_variant": 4096})
-        assert splits in plan and "launches=1\n" in plan and "finish=in_kernel" in plan, plan
+        assert "splits=4" in plan and "launches=1\n" in plan and "workspace_bytes=0" in plan, plan
         plan = mc.HostGraph(text=text, dims={"M": m, "N": n, "K": k}).launch_plan({"matmul": "tensor_core_bf16"})
-        assert splits in plan and "launches=2\n" in plan
+        assert ("splits=4" if m > 128 else "splits=2 tile_n=128") in plan and "launches=2\n" in plan, plan
 
 
 def test_auto_splits_k_where_whole_tiles_share_out_badly(mc):
