@@ -373,10 +373,9 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int n0 = (nb + s) * MC_TC_BN;
                 // The warp reads its slice of the region 32 columns at a time and finishes each piece (arithmetic,
-                // staging, stores) before it asks for the next. Reading the whole slice at once was measured to stall
-                // the next tile's MMAs for as long as the reads take (2.4 us per 256 x 256 tile, whatever K is):
-                // 32 TMEM loads issued together by the 8 warps hold up the MMAs behind them, 8 at a time do not. The
-                // region goes back to the MMA issuer when the last piece is in registers.
+                // staging, hand-over to the TMA unit) before it asks for the next: 32 live accumulator registers instead
+                // of 128. TMEM reads were measured to cost the running MMAs nothing. The region goes back to the MMA
+                // issuer when the last piece is in registers.
                 int last_chunk = -1;
 #pragma unroll
                 for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {

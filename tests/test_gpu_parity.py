@@ -399,6 +399,37 @@ def test_tensor_core_matmuls_within_their_precision_bounds(mc, oracle, name, ari
             check_bound(got, exact, abs_dot, k, u, sub, f"{name} {m}x{k}x{n} {layout} ran {kernels}")
 
 
+@pytest.mark.parametrize("name,u", [("tensor_core_bf16", 2.0 ** -8), ("tensor_core_f16", 2.0 ** -11), ("tensor_core_tf32", 2.0 ** -11)])
+def test_pair_kernel_writes_fp32_and_16_bit_copies_of_ragged_results_through_tma(mc, oracle, name, u):
+    """A matmul large enough for the SM-pair kernel whose result is both a graph output (FP32) and the left operand of a
+    second tensor-core matmul (16-bit copy): both forms leave the kernel as TMA stores of 32 x 32 boxes. Rows and
+    columns are no multiples of 32 (nor of the 128 x 256 tile), so boxes are clipped at both edges of both tensors; a
+    bias and relu ride in the first matmul's epilogue. Checked against the float64 bound per matmul, the second one
+    from the 16-bit rounding of the first one's GPU result."""
+    m, k, n, n2 = 2000, 520, 2296, 264
+    text = (f"input x : f32[{m}, {k}]\nconst w1 : f32[{k}, {n}] = uniform(seed=5, lo=-0.1, hi=0.1)\n"
+            f"const b1 : f32[{n}] = uniform(seed=6, lo=-0.5, hi=0.5)\nconst w2 : f32[{n}, {n2}] = uniform(seed=7, lo=-0.1, hi=0.1)\n"
+            "h0 = matmul x, w1\nh1 = add h0, b1\nh = relu h1\ny = matmul h, w2\noutput h\noutput y")
+    g, ins = oracle_inputs(oracle, text, seed=9)
+    consts = {node.name: np.asarray(node.value, dtype=np.float32).reshape(node.shape) for node in g.nodes if node.value is not None}
+    x = ins[0]
+    with mc.CompiledGraph(text=text, options={"matmul": name}) as exe:
+        plan = exe.matmul_kernels
+        h, y = exe.run(ins)
+        again = exe.run(ins)
+    assert np.array_equal(h, again[0]) and np.array_equal(y, again[1])
+    h, y = h.reshape(m, n), y.reshape(m, n2)
+    exact, abs_dot = exact_and_abs(x, consts["w1"])
+    pre = exact + consts["b1"].astype(np.float64)
+    want_h = np.maximum(pre, 0.0)
+    gamma = k * U32 / (1.0 - k * U32)
+    bound = (2.0 * u + u * u + 2.0 * gamma) * abs_dot + 4.0 * U32 * (np.abs(exact) + np.abs(consts["b1"])) + 2.0 * k * 2.0 ** -25
+    err = np.abs(h.astype(np.float64) - want_h)
+    assert (err <= bound).all(), f"{name} first matmul ({plan}): {int((err > bound).sum())} outside the bound, worst {err.max():.3e}"
+    exact2, abs2 = exact_and_abs(h, consts["w2"])  # from the GPU's own h: isolates the second matmul and its 16-bit operand
+    check_bound(y, exact2, abs2, n, u, True, f"{name} second matmul ({plan})")
+
+
 # -------------------------------------------------- the benchmark configs, small
 
 
