@@ -48,6 +48,9 @@ __device__ __forceinline__ void mc_tma_store_2d(const McTensorMap* map, unsigned
 // Until the bulk stores this thread has issued have read their shared-memory source.
 __device__ __forceinline__ void mc_tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
+// The same, but the most recent store may still be reading: enough to reuse the buffer of the store before it.
+__device__ __forceinline__ void mc_tma_store_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+
 // Shared-memory writes of this thread become visible to the TMA unit.
 __device__ __forceinline__ void mc_fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -352,6 +355,7 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
         const unsigned stage_base = bars_base + MC_TC2_BARRIER_BYTES + (unsigned)(warp - 2) * MC_TC2_STAGING_PER_WARP;
         int acc = 0;
         unsigned full_phase = 0;  // bit r: parity of region r's tmem_full barrier
+        unsigned buffer_turn = 0;  // which half of the staging buffer the next 2 KB box goes through
         bool ok = true;
         for (int item = cluster_id; ok && item < items; item += num_clusters) {
             int mp, nb, nsub, half;
@@ -416,6 +420,8 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                         // same kernel with the stores left out, or with the TMEM reads alone, ran at the MMA rate).
                         // TMA writes only the part of the box that lies inside the tensor, so ragged edges need no care.
                         if (p.c != nullptr) {
+                            // 128-byte rows of FP32 through the whole buffer, one box at a time (two boxes of 16 columns
+                            // taking turns in its halves measured slower on large problems: 8192^3 1551 against 1595)
                             if (lane == 0) mc_tma_store_wait_read();  // the previous box has left the buffer
                             __syncwarp();
 #pragma unroll
@@ -425,15 +431,21 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                             }
                             mc_fence_async_shared();
                             __syncwarp();
-                            if (lane == 0) mc_tma_store_2d(&map_c, stage_base, col0, row_base);
+                            if (lane == 0) {
+                                mc_tma_store_2d(&map_c, stage_base, col0, row_base);
+                                if (p.c16 != nullptr) mc_tma_store_wait_read();  // the 16-bit form goes through the same buffer next
+                            }
+                            __syncwarp();
                         }
                         if (p.c16 != nullptr) {
-                            if (lane == 0) mc_tma_store_wait_read();
+                            // 64-byte rows, 16-byte pieces XOR-ed with bits 1-2 of the row number (the 64-byte swizzle);
+                            // the 2 KB box takes turns with the one before it in the two halves of the buffer
+                            const unsigned half_buf = stage_base + (unsigned)(buffer_turn & 1) * 2048u;
+                            if (lane == 0) mc_tma_store_wait_read_but_one();
                             __syncwarp();
-                            // 64-byte rows, 16-byte pieces XOR-ed with bits 1-2 of the row number (the 64-byte swizzle)
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
-                                mc_st_shared_v4u(stage_base + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4),
+                                mc_st_shared_v4u(half_buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4),
                                                  mc_to_half2(f[8 * j + 0], f[8 * j + 1], p.c16_kind),
                                                  mc_to_half2(f[8 * j + 2], f[8 * j + 3], p.c16_kind),
                                                  mc_to_half2(f[8 * j + 4], f[8 * j + 5], p.c16_kind),
@@ -441,7 +453,8 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                             }
                             mc_fence_async_shared();
                             __syncwarp();
-                            if (lane == 0) mc_tma_store_2d(&map_c16, stage_base, col0, row_base);
+                            if (lane == 0) mc_tma_store_2d(&map_c16, half_buf, col0, row_base);
+                            ++buffer_turn;
                         }
                     } else if (row < p.m) {
                         if (p.c != nullptr) {
@@ -483,8 +496,9 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
             }
             acc ^= 1;
         }
-        // Every store this warp issued has completed before the CTA gives up its shared memory.
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        // Every store this warp issued has read its source before the CTA gives up its shared memory (the writes
+        // themselves complete with the grid, as for any other store).
+        if (lane == 0) mc_tma_store_wait_read();
     }
 
     __syncwarp();
