@@ -109,13 +109,18 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples for one GPU while the timed region runs."""
+    """nvidia-smi clock / throttle-reason samples for one GPU, every 20 ms, each with nvidia-smi's own time stamp.
+    It is started before the warm-up steps (nvidia-smi needs a moment to come up); the caller marks the wall-clock
+    window of the load, and only samples taken inside that window are summarised."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    QUERY = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    MIN_LOAD_S = 0.5  # a timed region shorter than this is followed by more of the same steps until it has lasted this long
 
     def __init__(self, index: int):
         self.index, self.lines, self.proc = index, [], None
+        self.window = None        # (begin, end of the timed region, end of the load) in time.time() seconds
+        self.timed_steps_only = True
 
     def start(self):
         try:
@@ -129,31 +134,59 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def wait_for_first_sample(self, limit_s: float = 3.0):
+        """Blocks until nvidia-smi has printed a sample (or the limit passes), so that the load is sampled from its start."""
+        t0 = time.time()
+        while self.proc is not None and not self.lines and time.time() - t0 < limit_s:
+            time.sleep(0.01)
+
+    @staticmethod
+    def _stamp(text):
+        import datetime
+        try:
+            return datetime.datetime.strptime(text, "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
-        sm, smax, power, reasons = [], [], [], set()
+        sm, smax, power, reasons, in_timed, sm_timed = [], [], [], set(), 0, []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.lines:
             f = [t.strip() for t in line.split(",")]
-            if len(f) < 9:
+            if len(f) < 10:
                 continue
+            stamp = self._stamp(f[0])
+            if self.window is not None:
+                if stamp is None or not (self.window[0] <= stamp <= self.window[2]):
+                    continue
             try:
-                sm.append(float(f[1]))
-                smax.append(float(f[2]))
+                sm.append(float(f[2]))
+                smax.append(float(f[3]))
             except ValueError:
                 continue
+            if self.window is not None and stamp <= self.window[1]:
+                in_timed += 1
+                sm_timed.append(sm[-1])
             try:
-                power.append(float(f[3]))
+                power.append(float(f[4]))
             except ValueError:
                 pass
-            for name, val in zip(names, f[5:9]):
+            for name, val in zip(names, f[6:10]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None}
+        out = {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+               "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None}
+        if self.window is not None:
+            out["samples_in_timed_region"] = in_timed
+            out["sm_mhz_timed_region"] = float(np.median(sm_timed)) if sm_timed else None
+            out["window"] = ("the timed region" if self.timed_steps_only else
+                             f"the timed region ({(self.window[1] - self.window[0]) * 1e3:.0f} ms) and the same steps repeated "
+                             f"right behind it, untimed, until {self.MIN_LOAD_S} s of load had passed")
+        return out
 
 
 def make_inputs(graph, dist, seed):
@@ -340,15 +373,18 @@ def main():
         stream = torch.cuda.Stream()
         launches_per_step = exe.kernel_launches
 
-        for _ in range(warmup):
-            exe.enqueue(stream.cuda_stream)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
+        for _ in range(warmup):
+            exe.enqueue(stream.cuda_stream)
+        torch.cuda.synchronize()
+        if rank == 0:
+            sampler.wait_for_first_sample()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        load_begin = time.time()
         # A working set that fits the 126 MB L2 would be served from it on every repeat: then each step is
         # timed on its own and a 256 MiB buffer is overwritten between steps to flush the cache.
         flush_l2 = exe.arena_bytes < (256 << 20)
@@ -374,6 +410,15 @@ def main():
             torch.cuda.synchronize()
             step_ms = [events[i].elapsed_time(events[i + 1]) for i in range(steps)]
         count1 = mc.lib().mcd_launch_count()
+        timed_end = time.time()
+        # nvidia-smi samples every 20 ms at best: a timed region of a few tens of milliseconds is followed, without a
+        # gap, by the same steps (untimed) so that the clocks under this load are seen by more than a sample or two.
+        while time.time() - load_begin < ClockSampler.MIN_LOAD_S:
+            sampler.timed_steps_only = False
+            for _ in range(max(1, steps // 4)):
+                exe.enqueue(stream.cuda_stream)
+            torch.cuda.synchronize()
+        sampler.window = (load_begin, timed_end, time.time())
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()

@@ -62,8 +62,22 @@ def test_clock_samples_are_summarised():
 
     sampler = bench.ClockSampler(0)
     sampler.proc = Finished()
-    sampler.lines = ["0, 1665, 1965, 998.21, 0x0000000000000004, Not Active, Not Active, Not Active, Active",
-                     "0, 1700, 1965, [N/A], 0x0, Not Active, Not Active, Not Active, Not Active", "not a sample"]
+    sampler.lines = ["2026/01/02 03:04:05.100, 0, 1665, 1965, 998.21, 0x0000000000000004, Not Active, Not Active, Not Active, Active",
+                     "2026/01/02 03:04:05.120, 0, 1700, 1965, [N/A], 0x0, Not Active, Not Active, Not Active, Not Active", "not a sample"]
     assert sampler.stop() == {"sm_mhz": 1682.5, "sm_max_mhz": 1965.0, "reasons": ["sw_power_cap"], "samples": 2, "power_w_max": 998.21}
+    # with the load's window marked, only the samples taken inside it count; those of the timed region are counted apart
+    import datetime
+    at = lambda text: datetime.datetime.strptime(text, "%Y/%m/%d %H:%M:%S.%f").timestamp()
+    windowed = bench.ClockSampler(0)
+    windowed.proc = Finished()
+    windowed.lines = ["2026/01/02 03:04:04.900, 0, 1965, 1965, 150.0, 0x0, Not Active, Not Active, Not Active, Not Active"] + sampler.lines + [
+        "2026/01/02 03:04:05.300, 0, 1500, 1965, 990.0, 0x4, Not Active, Not Active, Not Active, Active",
+        "2026/01/02 03:04:06.000, 0, 1965, 1965, 140.0, 0x0, Not Active, Not Active, Not Active, Not Active"]
+    windowed.window = (at("2026/01/02 03:04:05.000"), at("2026/01/02 03:04:05.200"), at("2026/01/02 03:04:05.500"))
+    windowed.timed_steps_only = False
+    got = windowed.stop()
+    assert got["samples"] == 3 and got["samples_in_timed_region"] == 2 and got["sm_mhz"] == 1665.0 and got["power_w_max"] == 998.21
+    assert got["sm_mhz_timed_region"] == 1682.5
+    assert got["reasons"] == ["sw_power_cap"] and "repeated" in got["window"]
     idle = bench.ClockSampler(0)
     assert idle.stop()["reasons"] == ["nvidia-smi unavailable"]
