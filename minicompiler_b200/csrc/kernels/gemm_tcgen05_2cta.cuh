@@ -421,7 +421,7 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
                         // TMA writes only the part of the box that lies inside the tensor, so ragged edges need no care.
                         if (p.c != nullptr) {
                             // 128-byte rows of FP32 through the whole buffer, one box at a time (two boxes of 16 columns
-                            // taking turns in its halves measured slower on large problems: 8192^3 1551 against 1595)
+                            // taking turns in its halves measured no faster: 8192^3 1536 against 1538 TFLOP/s on one box)
                             if (lane == 0) mc_tma_store_wait_read();  // the previous box has left the buffer
                             __syncwarp();
 #pragma unroll
