@@ -532,8 +532,13 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
         } else {
             p.staged = 0;
         }
+        // The pair kernels are launched as programmatic dependents of whatever precedes them in the stream: their CTAs
+        // may start on SMs the previous grid has left (it says so early if it is one of these kernels; any other kernel
+        // does by ending) and wait for that grid to complete before they touch global memory. Variant bit 32768: plain.
+        const bool dependent = (a->variant & 32768) == 0;
         if (a->function != nullptr) {
             void* params[] = {&map_a, &map_b, &map_c, &map_c16, &p, &epi};
+            if (dependent) return mcd_launch_dependent(a->function, pair_grid, MC_TC_THREADS, MC_TC2_SMEM_BYTES, s, params);
             return mcd_launch(a->function, pair_grid, 1, 1, MC_TC_THREADS, MC_TC2_SMEM_BYTES, s, params);
         }
         using PairKernel = void (*)(const McTensorMap, const McTensorMap, const McTensorMap, const McTensorMap, const McTcParams,
@@ -552,6 +557,21 @@ int gemm_tc(const mcd_gemm_args* a, cudaStream_t s) {
                     return rc;
                 }
             }
+        }
+        if (dependent) {
+            cudaLaunchAttribute attribute;
+            attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attribute.val.programmaticStreamSerializationAllowed = 1;
+            cudaLaunchConfig_t config = {};
+            config.gridDim = dim3(pair_grid, 1, 1);
+            config.blockDim = dim3(MC_TC_THREADS, 1, 1);
+            config.dynamicSmemBytes = MC_TC2_SMEM_BYTES;
+            config.stream = s;
+            config.attrs = &attribute;
+            config.numAttrs = 1;
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            return check_rt(cudaLaunchKernelEx(&config, kernel, map_a, map_b, map_c, map_c16, p, epi),
+                            "cudaLaunchKernelEx(mc_gemm_tc2, dependent)");
         }
         kernel<<<pair_grid, MC_TC_THREADS, MC_TC2_SMEM_BYTES, s>>>(map_a, map_b, map_c, map_c16, p, epi);
         return launched("mc_gemm_tc2");

@@ -124,6 +124,9 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // The launch behind this one may take its place as soon as SMs fall free (a kernel launched as a programmatic
+    // dependent, e.g. the next layer of a stack): its CTAs set themselves up while the last tiles of this grid finish.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const unsigned rank = mc_cluster_ctarank();
     const bool leader = rank == 0;
     const int cluster_id = blockIdx.x >> 1;
@@ -162,6 +165,10 @@ __device__ __forceinline__ void mc_gemm_tc2_body(const McTensorMap& map_a, const
     mc_cluster_sync();  // both CTAs' barriers are initialised before either signals the other's
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = tmem_base_slot;
+    // Launched as a programmatic dependent, this grid may have started before the one in front of it was done: nothing
+    // is read from or written to global memory before that grid has completed and its writes are visible (a no-op for
+    // a plain launch). Barriers, TMEM and the tensor maps in the parameters are set up by then.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // Work item -> row pair `mp`, first 256-column block `nb`, number of 256-column tiles `nsub` (0: nothing to
     // do), and `half` = 0 / 1 when the item is a 128-column half of a normal tile (-1 otherwise).
