@@ -205,10 +205,15 @@ typedef struct mcd_gemm_args {
     const float* epilogue_inputs[MCD_MAX_EPILOGUE_INPUTS];
     int num_epilogue_inputs;
     unsigned int* status; /* device word: a kernel that gives up a bounded wait ORs an error code in */
-    int variant;          /* tuning variant, 0 = default; bit 64: split tensor-core matmuls add their partial tiles inside
-                             thread-block clusters instead of through the workspace and a second launch */
-    int tile_n;           /* tensor-core arithmetic: columns per tile, 0 or 256 = default, 128 or 64 = narrow tiles
-                             for small unsplit problems (one-CTA kernel) */
+    int variant;          /* tuning variant, 0 = default. Bits: 2 no half-tile tails; 4 never / 8 always the SM-pair
+                             kernel; 16 always / 32 never its two-tile form; 64 split tensor-core matmuls add their
+                             partial tiles inside thread-block clusters instead of through the workspace and a second
+                             launch; 128 outputs stored from registers instead of through the TMA unit; 512 never /
+                             1024 always the TMA-fed FP32 kernel; 2048 the split-K reduction as a plain launch;
+                             32768 the SM-pair kernels as plain launches (default: programmatic dependents of the
+                             launch in front of them) */
+    int tile_n;           /* tensor-core arithmetic: columns per tile, 0 or 256 = default, 128 or 64 = narrower tiles
+                             (one-CTA kernel): small unsplit problems, and single rows of tiles with fewer K slices */
     int has_epilogue;     /* non-zero when the launch carries a generated epilogue; set it before asking for the
                              entry point as well, kernel selection depends on it */
 } mcd_gemm_args;
